@@ -1,0 +1,89 @@
+/*
+ * Quantized GEMM entry points: FP8 with fine-grained fp32 scales, and int4
+ * weight-only with 16-bit activations.
+ *
+ * Replaces the two quantized entries of include/kernel_set/gemm.h of the
+ * reference project (ks_gemm_w4a16 at :51-59, ks_gemm_fp8_blockwise at
+ * :79-98). The dense / int8 / per-token-fp8 / nvfp4 GEMMs of that header are
+ * a different code path and are not exported by this library.
+ *
+ * All matrices are row-major and dense (row stride = number of columns). All
+ * pointers are device pointers. Calls enqueue work on `stream` and return
+ * without synchronising.
+ */
+#ifndef KERNEL_SET_GEMM_H_
+#define KERNEL_SET_GEMM_H_
+
+#include "kernel_set/types.h"
+
+KS_BEGIN_EXTERN_C
+
+/*
+ * C[M,N] = A[M,K] . W[K,N] + bias,  W[k,n] = (q[k,n] - zero[g,n]) * scale[g,n],
+ * g = k / group_size.
+ *
+ *   a         [M,K]      f16 or bf16 (`dtype`)
+ *   b_packed  [K/2,N]    uint8; low nibble holds the code of the even k, high
+ *                        nibble the code of the odd k; codes are 0..15
+ *   scales    [K/gs,N]   `dtype`
+ *   zeros     [K/gs,N]   `dtype`, in code units (8.0 for a symmetric grid);
+ *                        NULL means zero-point 0
+ *   bias      [N]        `dtype` or NULL
+ *   group_size <= 0 means one group spanning all of K.
+ *
+ * K must be even and group_size must divide K (UNSUPPORTED_SHAPE otherwise);
+ * dtype other than f16/bf16 is UNSUPPORTED_DTYPE.
+ * Same contract as the reference: gemm.h:51-59, gemm_w4a16.cu:6-19,151-182.
+ */
+KS_API ks_status_t ks_gemm_w4a16(void* c, const void* a, const void* b_packed,
+                                 const void* scales, const void* zeros,
+                                 const void* bias, int64_t m, int64_t n,
+                                 int64_t k, int group_size, ks_dtype_t dtype,
+                                 ks_stream_t stream);
+
+/*
+ * out[m,n] = sum over K-blocks kb of
+ *            a_scale[m,kb] * b_scale[kb, n/block_n] * sum_{k in kb} A8[m,k]*B8[k,n]
+ * with the inner sum and the outer sum both kept in fp32.
+ *
+ *   a_fp8    [M,K]                         e4m3 or e5m2 (`fp8_dtype`)
+ *   b_fp8    [K,N]                         same fp8 type
+ *   a_scale  [M, ceil(K/block_k)]          fp32, one per 1 x block_k strip
+ *   b_scale  [ceil(K/block_k), ceil(N/block_n)]  fp32, one per weight block
+ *   out      [M,N]                         f32 / f16 / bf16 (`out_dtype`)
+ *
+ * M, N, K need not be multiples of the block sizes. block_n = block_k = 128
+ * with K and N multiples of 16 takes the tcgen05 kernel; every other legal
+ * combination takes a slower general kernel with the same results.
+ * Same contract as the reference: gemm.h:79-98, gemm_fp8_blockwise.cu:218-302.
+ */
+KS_API ks_status_t ks_gemm_fp8_blockwise(void* out, const void* a_fp8,
+                                         const void* b_fp8,
+                                         const float* a_scale,
+                                         const float* b_scale, int64_t m,
+                                         int64_t n, int64_t k, int block_n,
+                                         int block_k, ks_dtype_t fp8_dtype,
+                                         ks_dtype_t out_dtype,
+                                         ks_stream_t stream);
+
+/*
+ * Same product with the weight stored the way checkpoints hold it:
+ *   b_fp8    [N,K]                               (one row per output column)
+ *   b_scale  [ceil(N/block_n), ceil(K/block_k)]
+ * Everything else as ks_gemm_fp8_blockwise. The reference has no C entry for
+ * this layout; its Python router reaches it through an external provider
+ * (bindings/python/kernel_set/backends/_registry.py:416-424), so this symbol
+ * is an addition, not a replacement.
+ */
+KS_API ks_status_t ks_gemm_fp8_blockwise_nt(void* out, const void* a_fp8,
+                                            const void* b_fp8,
+                                            const float* a_scale,
+                                            const float* b_scale, int64_t m,
+                                            int64_t n, int64_t k, int block_n,
+                                            int block_k, ks_dtype_t fp8_dtype,
+                                            ks_dtype_t out_dtype,
+                                            ks_stream_t stream);
+
+KS_END_EXTERN_C
+
+#endif /* KERNEL_SET_GEMM_H_ */

@@ -1,0 +1,65 @@
+/*
+ * Activation quantizer and int4 weight format helpers.
+ *
+ * Replaces three entries of include/kernel_set/quant.h of the reference
+ * project: ks_quantize_fp8_group (:28-40), ks_dequantize_int4 (:53-58) and
+ * ks_repack_int4 (:60-66). The per-tensor fp8, int8 and nvfp4 quantizers of
+ * that header are other formats and are not exported here.
+ */
+#ifndef KERNEL_SET_QUANT_H_
+#define KERNEL_SET_QUANT_H_
+
+#include "kernel_set/types.h"
+
+KS_BEGIN_EXTERN_C
+
+/*
+ * For every row r and every run g of `group_size` consecutive columns (the
+ * last run of a row may be shorter):
+ *     amax        = max |input[r,c]| over the run, in fp32
+ *     scale[r,g]  = max(amax / qmax, 1e-12)      qmax = 448 (e4m3), 57344 (e5m2)
+ *     out[r,c]    = fp8(input[r,c] / scale[r,g]) round-to-nearest-even, saturating
+ *
+ *   input  [rows, cols]                     f32 / f16 / bf16 (`in_dtype`)
+ *   out    [rows, cols]                     `fp8_dtype`
+ *   scale  [rows, ceil(cols/group_size)]    fp32, row-major
+ *
+ * Both divisions are IEEE divisions, which is what the reference's torch
+ * statement of the op computes (benchmarks/bench.py:1444-1457, 2339-2344).
+ * Contract otherwise as the reference: quant.h:28-40, quant_fp8_group.cu:133-214.
+ */
+KS_API ks_status_t ks_quantize_fp8_group(void* out, float* scale,
+                                         const void* input, int64_t rows,
+                                         int64_t cols, int group_size,
+                                         ks_dtype_t in_dtype,
+                                         ks_dtype_t fp8_dtype,
+                                         ks_stream_t stream);
+
+/*
+ * out[k,n] = (q[k,n] - zeros[k/gs, n]) * scales[k/gs, n], computed in fp32 and
+ * rounded once to `out_dtype` (f32 / f16 / bf16).
+ *
+ *   qweight_packed  [K/8, N] int32; code of k = 8*row + j sits in bits 4j..4j+3
+ *   scales, zeros   [K/gs, N] `out_dtype`; both required
+ *   K multiple of 8 and of group_size.
+ * Contract as the reference: quant.h:53-58, dequant_int4.cu:78-112.
+ */
+KS_API ks_status_t ks_dequantize_int4(void* out, const void* qweight_packed,
+                                      const void* scales, const void* zeros,
+                                      int64_t k, int64_t n, int group_size,
+                                      ks_dtype_t out_dtype, ks_stream_t stream);
+
+/*
+ * Re-lays the int32 [K/8, N] packing above into the uint8 [K/2, N] packing
+ * that ks_gemm_w4a16 reads (even k in the low nibble). `num_bits` must be 4;
+ * a non-NULL `perm` (activation reordering) returns KS_ERROR_NOT_IMPLEMENTED.
+ * Contract as the reference: quant.h:60-66, repack_int4.cu:43-70.
+ */
+KS_API ks_status_t ks_repack_int4(void* out_packed, const void* qweight,
+                                  const void* perm, int64_t size_k,
+                                  int64_t size_n, int num_bits,
+                                  ks_stream_t stream);
+
+KS_END_EXTERN_C
+
+#endif /* KERNEL_SET_QUANT_H_ */

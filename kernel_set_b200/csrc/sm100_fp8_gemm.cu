@@ -1,0 +1,503 @@
+// FP8 block-scaled GEMM for sm_100a: TMA-fed shared-memory ring, tcgen05.mma
+// (kind::f8f6f4) into double-buffered TMEM partials, and an fp32 promotion of
+// every 128-deep K-block partial by a_scale * b_scale in the epilogue warps.
+//
+// Computes what ks_gemm_fp8_blockwise / _nt / ks_moe_grouped_gemm_fp8_blockwise
+// declare, for block_n = block_k = 128 (reference algebra:
+// kernels/src/gemm/gemm_fp8_blockwise.cu:107-150 — an fp32 inner product per
+// K-block, folded into the fp32 output with the block's scale product).
+//
+// CTA anatomy (one CTA per SM, persistent over output tiles of 128 x BN):
+//   warp 0      TMA producer: A tile 128 x 128 B and B tile BN x 128 B per stage,
+//               128-byte swizzle, completion counted on the stage's `full` barrier
+//   warp 1      MMA issuer: 4 UMMAs (M128, N=BN, K32) per K-block into TMEM buffer
+//               kb & 1; tcgen05.commit releases the stage and publishes the partial
+//   warps 2..   epilogue: warp w reads TMEM lanes 32*(w%4).. and 128 columns,
+//               acc = fma(partial, a_scale[row,kb] * b_scale[kb,nb], acc) in
+//               registers, frees the TMEM buffer, and after the last K-block
+//               rounds once to the output type and stores its row segment
+// B may be stored [N,K] (K-major UMMA operand) or [K,N] (MN-major operand, the
+// layout of the reference C ABI); both are loaded by TMA without a transpose.
+//
+// Roofline: tensor-bound for M >= ~1024 (2*M*N*K flop over 4.5 PFLOP/s dense
+// FP8); bytes per launch M*K + N*K + M*N*sizeof(out) + scales.
+#include <mutex>
+
+#include "common.cuh"
+#include "sm100_fp8_gemm.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ksb {
+namespace sm100 {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 128;
+constexpr int kMaxExperts = 1024;
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = kBM * kBK;
+  static constexpr int kBBytes = BN * kBK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kEpiWarps = (BN / 128) * 4;
+  static constexpr int kThreads = 64 + kEpiWarps * 32;
+  static constexpr int kTmemCols = 2 * BN;
+  // ring + 1024 B alignment slack + barriers/flags + grouped tile prefix and offsets
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + 2 * 4 * (kMaxExperts + 1);
+};
+
+struct Params {
+  void* out;
+  const float* a_scale;
+  const float* b_scale;
+  const int32_t* offsets;  // [E+1] when grouped
+  unsigned int* fault_word;
+  int num_experts;
+  int m;        // rows of A (all experts together when grouped)
+  int n, k;
+  int nkb, nnb;
+  int tiles_n;
+  int tiles_m;  // dense only
+  uint32_t idesc;
+  int vec_store;  // 16-byte output stores are legal
+};
+
+struct TileCoord {
+  int expert, row0, row_end, n0;
+};
+
+template <int BN, bool GROUPED>
+__device__ __forceinline__ bool locate_tile(const Params& p, const int* prefix, const int* offs, int t,
+                                            TileCoord* tc) {
+  if constexpr (!GROUPED) {
+    if (t >= p.tiles_m * p.tiles_n) return false;
+    const int mt = t / p.tiles_n;
+    tc->expert = 0;
+    tc->row0 = mt * kBM;
+    tc->row_end = p.m;
+    tc->n0 = (t - mt * p.tiles_n) * BN;
+    return true;
+  } else {
+    const int total_mt = prefix[p.num_experts];
+    if (t >= total_mt * p.tiles_n) return false;
+    const int mt = t / p.tiles_n;
+    int lo = 0, hi = p.num_experts - 1;  // last e with prefix[e] <= mt
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (prefix[mid] <= mt) lo = mid; else hi = mid - 1;
+    }
+    tc->expert = lo;
+    tc->row0 = offs[lo] + (mt - prefix[lo]) * kBM;
+    tc->row_end = offs[lo + 1];
+    tc->n0 = (t - mt * p.tiles_n) * BN;
+    return true;
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_16(OutT* dst, const float* v, bool vec, int valid_cols);
+
+// Stores 16 consecutive outputs of one row; `valid_cols` of them exist.
+template <>
+__device__ __forceinline__ void store_16<float>(float* dst, const float* v, bool vec, int valid_cols) {
+  if (vec && valid_cols >= 16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i < valid_cols) dst[i] = v[i];
+  }
+}
+template <>
+__device__ __forceinline__ void store_16<__nv_bfloat16>(__nv_bfloat16* dst, const float* v, bool vec,
+                                                        int valid_cols) {
+  if (vec && valid_cols >= 16) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i < valid_cols) dst[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+template <>
+__device__ __forceinline__ void store_16<__half>(__half* dst, const float* v, bool vec, int valid_cols) {
+  if (vec && valid_cols >= 16) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i < valid_cols) dst[i] = __float2half_rn(v[i]);
+  }
+}
+
+template <int BN, bool NT, bool GROUPED, typename OutT>
+__global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
+fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                          const Params p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t ring = (raw_addr + 1023u) & ~1023u;  // 1024-byte aligned for the 128 B swizzle
+  uint8_t* ctrl = smem_raw + (ring - raw_addr) + C::kStages * C::kStageBytes;
+  const uint32_t ctrl_addr = ring + C::kStages * C::kStageBytes;
+  // control block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem slot | abort flag
+  const uint32_t bar_full = ctrl_addr;
+  const uint32_t bar_empty = ctrl_addr + 8 * C::kStages;
+  const uint32_t bar_tfull = ctrl_addr + 16 * C::kStages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * C::kStages + 32);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  int* prefix = reinterpret_cast<int*>(ctrl + 256);
+  int* offs = prefix + (kMaxExperts + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const WaitCtx wctx{abort_flag, p.fault_word};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, C::kEpiWarps);
+    }
+    *abort_flag = 0u;
+    fence_barrier_init();
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+    tmem_relinquish();
+  }
+  if constexpr (GROUPED) {
+    for (int e = threadIdx.x; e <= p.num_experts; e += blockDim.x) offs[e] = p.offsets[e];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int run = 0;
+      for (int e = 0; e < p.num_experts; ++e) {
+        prefix[e] = run;
+        const int rows = offs[e + 1] - offs[e];
+        run += rows > 0 ? (rows + kBM - 1) / kBM : 0;
+      }
+      prefix[p.num_experts] = run;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    uint32_t it = 0;
+    bool ok = true;
+    TileCoord tc;
+    for (int t = blockIdx.x; ok && locate_tile<BN, GROUPED>(p, prefix, offs, t, &tc); t += gridDim.x) {
+      for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+        const uint32_t s = it % C::kStages;
+        const uint32_t ph = (it / C::kStages) & 1u;
+        if (!mbar_wait(wctx, bar_empty + 8 * s, ph ^ 1u, 0x100u + s)) { ok = false; break; }
+        if (lane == 0) {
+          const uint32_t full = bar_full + 8 * s;
+          const uint32_t a_dst = ring + s * C::kStageBytes;
+          const uint32_t b_dst = a_dst + C::kABytes;
+          mbar_arrive_expect_tx(full, C::kStageBytes);
+          tma_load_2d(a_dst, &tm_a, full, kb * kBK, tc.row0);
+          if constexpr (NT) {
+            tma_load_3d(b_dst, &tm_b, full, kb * kBK, tc.n0, tc.expert);
+          } else {
+#pragma unroll
+            for (int h = 0; h < BN / 128; ++h)
+              tma_load_3d(b_dst + h * (128 * kBK), &tm_b, full, tc.n0 + h * 128, kb * kBK, tc.expert);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    uint32_t it = 0;
+    bool ok = true;
+    TileCoord tc;
+    for (int t = blockIdx.x; ok && locate_tile<BN, GROUPED>(p, prefix, offs, t, &tc); t += gridDim.x) {
+      for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+        const uint32_t s = it % C::kStages;
+        const uint32_t ph = (it / C::kStages) & 1u;
+        const uint32_t buf = it & 1u;
+        const uint32_t aph = (it >> 1) & 1u;
+        if (!mbar_wait(wctx, bar_tempty + 8 * buf, aph ^ 1u, 0x200u + buf)) { ok = false; break; }
+        if (!mbar_wait(wctx, bar_full + 8 * s, ph, 0x300u + s)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t a_src = ring + s * C::kStageBytes;
+          const uint32_t b_src = a_src + C::kABytes;
+          const uint32_t d_tmem = tmem_base + buf * BN;
+#pragma unroll
+          for (int kk = 0; kk < kBK / 32; ++kk) {
+            // A and (NT) B are K-major: 8-row groups 1024 B apart, a K step of 32
+            // elements is 32 B inside the swizzle atom. B stored [K,N] is MN-major:
+            // 128-column atoms 16 KB apart, 8-k groups 1024 B apart, a K step of 32
+            // rows is 32 * 128 B.
+            const uint64_t a_desc = umma_smem_desc_sw128(a_src + kk * 32, 16, 1024);
+            const uint64_t b_desc = NT ? umma_smem_desc_sw128(b_src + kk * 32, 16, 1024)
+                                       : umma_smem_desc_sw128(b_src + kk * 32 * 128, 128 * kBK, 1024);
+            umma_f8f6f4(d_tmem, a_desc, b_desc, p.idesc, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(bar_empty + 8 * s);
+          tc_commit(bar_tfull + 8 * buf);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int quarter = warp & 3;         // TMEM lane quarter this warp can address
+    const int half = (warp - 2) >> 2;     // 128-column half of the tile
+    const int row_in_tile = quarter * 32 + lane;
+    OutT* out = static_cast<OutT*>(p.out);
+    uint32_t it = 0;
+    bool ok = true;
+    TileCoord tc;
+    for (int t = blockIdx.x; ok && locate_tile<BN, GROUPED>(p, prefix, offs, t, &tc); t += gridDim.x) {
+      const int row = tc.row0 + row_in_tile;
+      const bool row_ok = row < tc.row_end;
+      const int col0 = tc.n0 + half * 128;
+      int nb = col0 >> 7;
+      if (nb > p.nnb - 1) nb = p.nnb - 1;
+      const float* as_ptr = p.a_scale + static_cast<size_t>(row_ok ? row : 0) * p.nkb;
+      const float* bs_ptr = p.b_scale + static_cast<size_t>(tc.expert) * p.nkb * p.nnb +
+                            (NT ? static_cast<size_t>(nb) * p.nkb : static_cast<size_t>(nb));
+      const size_t bs_step = NT ? 1 : static_cast<size_t>(p.nnb);
+
+      float acc[128];
+#pragma unroll
+      for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+      float as_next = row_ok ? __ldg(as_ptr) : 0.f;
+      float bs_next = __ldg(bs_ptr);
+
+      for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+        const float scale = as_next * bs_next;
+        if (kb + 1 < p.nkb) {
+          as_next = row_ok ? __ldg(as_ptr + kb + 1) : 0.f;
+          bs_next = __ldg(bs_ptr + static_cast<size_t>(kb + 1) * bs_step);
+        }
+        const uint32_t buf = it & 1u;
+        const uint32_t aph = (it >> 1) & 1u;
+        if (!mbar_wait(wctx, bar_tfull + 8 * buf, aph, 0x400u + buf)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + half * 128;
+        uint32_t r0[16], r1[16];
+        tmem_ld_x16(taddr, r0);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          tmem_wait_ld();
+          if (c < 7) {
+            if (c & 1) tmem_ld_x16(taddr + (c + 1) * 16, r0);
+            else tmem_ld_x16(taddr + (c + 1) * 16, r1);
+          } else {
+            // every column of this warp's slice is in registers: hand the buffer back
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float v = __uint_as_float((c & 1) ? r1[j] : r0[j]);
+            acc[c * 16 + j] = fmaf(v, scale, acc[c * 16 + j]);
+          }
+        }
+      }
+      if (ok && row_ok) {
+        OutT* dst = out + static_cast<size_t>(row) * p.n + col0;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int valid = p.n - (col0 + c * 16);
+          if (valid > 0) store_16<OutT>(dst + c * 16, &acc[c * 16], p.vec_store != 0, valid);
+        }
+      }
+    }
+  }
+
+  // ------------------------------- teardown -------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    // A wait gave up: give copies and MMAs still in flight time to land
+    // before shared memory and TMEM are released.
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------- host side --------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    cudaGetLastError();
+  });
+  return fn;
+}
+
+// Byte tensor of rank 2 or 3 (innermost first), 128-byte swizzled boxes.
+bool encode_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+               const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t gdim[3];
+  cuuint64_t gstr[2];
+  cuuint32_t bdim[3];
+  cuuint32_t estr[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bdim[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
+                        gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int BN, bool NT, bool GROUPED, typename OutT>
+ks_status_t launch_one(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUtensorMap& tm_b, const Params& p,
+                       int grid, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  auto kernel = fp8_blockwise_umma_kernel<BN, NT, GROUPED, OutT>;
+  static std::mutex mu;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+      if (e != cudaSuccess) return cuda_status(e, a.where);
+      attr_done[dev] = true;
+    }
+  }
+  kernel<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tm_a, tm_b, p);
+  return cuda_status(cudaGetLastError(), a.where);
+}
+
+template <int BN, bool NT, bool GROUPED>
+ks_status_t launch_out(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUtensorMap& tm_b, const Params& p,
+                       int grid, cudaStream_t stream) {
+  switch (a.out_dtype) {
+    case KS_DTYPE_F32: return launch_one<BN, NT, GROUPED, float>(a, tm_a, tm_b, p, grid, stream);
+    case KS_DTYPE_F16: return launch_one<BN, NT, GROUPED, __half>(a, tm_a, tm_b, p, grid, stream);
+    default: return launch_one<BN, NT, GROUPED, __nv_bfloat16>(a, tm_a, tm_b, p, grid, stream);
+  }
+}
+
+template <int BN>
+ks_status_t launch_bn(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUtensorMap& tm_b, const Params& p,
+                      int grid, cudaStream_t stream) {
+  const bool grouped = a.offsets != nullptr;
+  if (a.nt) return grouped ? launch_out<BN, true, true>(a, tm_a, tm_b, p, grid, stream)
+                           : launch_out<BN, true, false>(a, tm_a, tm_b, p, grid, stream);
+  return grouped ? launch_out<BN, false, true>(a, tm_a, tm_b, p, grid, stream)
+                 : launch_out<BN, false, false>(a, tm_a, tm_b, p, grid, stream);
+}
+
+}  // namespace
+
+bool fp8_blockwise_eligible(const Fp8GemmArgs& a) {
+  if (a.block_n != 128 || a.block_k != 128) return false;
+  if (a.k % 16 != 0) return false;
+  if (!a.nt && a.n % 16 != 0) return false;
+  if (!aligned16(a.a) || !aligned16(a.b)) return false;
+  if (a.m > INT32_MAX / 2 || a.n > INT32_MAX / 2 || a.k > INT32_MAX / 2) return false;
+  if (a.offsets != nullptr && (a.num_experts > kMaxExperts || a.num_experts < 1)) return false;
+  return encode_fn() != nullptr;
+}
+
+ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
+  const bool grouped = a.offsets != nullptr;
+  const int experts = grouped ? a.num_experts : 1;
+  const int sms = sm_count();
+  const int64_t tiles_m_bound = grouped ? (a.m + kBM - 1) / kBM + experts : (a.m + kBM - 1) / kBM;
+  // Wide tiles halve the shared-memory traffic per flop; use them once they
+  // still give every SM a tile.
+  const int64_t tiles256 = tiles_m_bound * ((a.n + 255) / 256);
+  const int bn = (a.force_bn == 128 || a.force_bn == 256) ? a.force_bn : (tiles256 >= sms ? 256 : 128);
+
+  CUtensorMap tm_a, tm_b;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.m)};
+    const uint64_t str[1] = {static_cast<uint64_t>(a.k)};
+    const uint32_t box[2] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(kBM)};
+    if (!encode_u8(&tm_a, a.a, 2, dims, str, box))
+      KSB_FAIL(KS_ERROR_INTERNAL, std::string(a.where) + ": tensor map for A rejected");
+  }
+  if (a.nt) {
+    const uint64_t dims[3] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.n), static_cast<uint64_t>(experts)};
+    const uint64_t str[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.k) * static_cast<uint64_t>(a.n)};
+    const uint32_t box[3] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(bn), 1u};
+    if (!encode_u8(&tm_b, a.b, 3, dims, str, box))
+      KSB_FAIL(KS_ERROR_INTERNAL, std::string(a.where) + ": tensor map for B rejected");
+  } else {
+    const uint64_t dims[3] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k), static_cast<uint64_t>(experts)};
+    const uint64_t str[2] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k) * static_cast<uint64_t>(a.n)};
+    const uint32_t box[3] = {128u, static_cast<uint32_t>(kBK), 1u};
+    if (!encode_u8(&tm_b, a.b, 3, dims, str, box))
+      KSB_FAIL(KS_ERROR_INTERNAL, std::string(a.where) + ": tensor map for B rejected");
+  }
+
+  Params p;
+  p.out = a.out;
+  p.a_scale = a.a_scale;
+  p.b_scale = a.b_scale;
+  p.offsets = a.offsets;
+  p.fault_word = kernel_fault_word();
+  p.num_experts = experts;
+  p.m = static_cast<int>(a.m);
+  p.n = static_cast<int>(a.n);
+  p.k = static_cast<int>(a.k);
+  p.nkb = static_cast<int>((a.k + kBK - 1) / kBK);
+  p.nnb = static_cast<int>((a.n + 127) / 128);
+  p.tiles_n = static_cast<int>((a.n + bn - 1) / bn);
+  p.tiles_m = static_cast<int>((a.m + kBM - 1) / kBM);
+  const uint32_t fmt = a.e5m2 ? 1u : 0u;
+  p.idesc = umma_instr_desc(fmt, fmt, 0u, a.nt ? 0u : 1u, kBM, static_cast<uint32_t>(bn));
+  const size_t out_elt = a.out_dtype == KS_DTYPE_F32 ? 4 : 2;
+  p.vec_store = (aligned16(a.out) && (static_cast<size_t>(a.n) * out_elt) % 16 == 0) ? 1 : 0;
+
+  int64_t tiles = tiles_m_bound * p.tiles_n;
+  const int grid = static_cast<int>(tiles < sms ? (tiles < 1 ? 1 : tiles) : sms);
+  return bn == 256 ? launch_bn<256>(a, tm_a, tm_b, p, grid, stream) : launch_bn<128>(a, tm_a, tm_b, p, grid, stream);
+}
+
+}  // namespace sm100
+}  // namespace ksb

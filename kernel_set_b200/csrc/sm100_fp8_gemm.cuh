@@ -1,0 +1,37 @@
+// Host interface of the tcgen05 FP8 block-scaled GEMM (dense and grouped).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernel_set/types.h"
+
+namespace ksb {
+namespace sm100 {
+
+struct Fp8GemmArgs {
+  const char* where = "";          // entry-point name for error messages
+  void* out = nullptr;             // [m, n] out_dtype
+  const void* a = nullptr;         // [m, k] fp8
+  const void* b = nullptr;         // nt: [E][n, k]; else [E][k, n]
+  const float* a_scale = nullptr;  // [m, ceil(k/128)]
+  const float* b_scale = nullptr;  // nt: [E][ceil(n/128), ceil(k/128)]; else transposed
+  const int32_t* offsets = nullptr;  // [E+1] row boundaries; NULL = one dense problem
+  int num_experts = 1;
+  int64_t m = 0, n = 0, k = 0;     // m = all rows (all experts together)
+  int block_n = 128, block_k = 128;
+  bool nt = false;
+  bool e5m2 = false;
+  ks_dtype_t out_dtype = KS_DTYPE_BF16;
+  int force_bn = 0;                // 128 / 256 pins the tile width (tests), 0 = choose
+};
+
+// True when the tcgen05 kernel can take the problem (128 x 128 scale blocks,
+// TMA-legal strides and alignment, driver entry point available).
+bool fp8_blockwise_eligible(const Fp8GemmArgs& a);
+
+// Encodes the tensor maps and enqueues one persistent launch on `stream`.
+ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream);
+
+}  // namespace sm100
+}  // namespace ksb

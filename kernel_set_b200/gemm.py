@@ -1,0 +1,50 @@
+"""Out-parameter wrappers of the quantized GEMM entry points; signatures of
+``bindings/python/kernel_set/gemm.py`` of the reference project
+(``gemm_w4a16`` ``:196-225``, ``gemm_fp8_blockwise`` ``:313-362``)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ._lib import check, lib
+from ._tensor import TensorLike, default_stream, dtype_to_ks, f32_ptr, infer_dtype, ptr
+
+
+def gemm_w4a16(c: TensorLike, a: TensorLike, b_packed: TensorLike, scales: TensorLike, zeros: TensorLike,
+               m: int, n: int, k: int, group_size: int, bias: TensorLike = None,
+               dtype: Optional[int] = None, stream: TensorLike = None) -> TensorLike:
+    """``C[M,N] = A[M,K] @ dequant(b_packed)`` (+ ``bias``): ``b_packed`` uint8
+    ``[K/2,N]`` (even k in the low nibble), ``scales``/``zeros``
+    ``[K/group_size,N]`` in the activation dtype, ``zeros`` may be ``None``."""
+    dt = infer_dtype(a, dtype)
+    check(lib.ks_gemm_w4a16(ptr(c, name="c"), ptr(a, name="a"), ptr(b_packed, name="b_packed"),
+                            ptr(scales, name="scales"), ptr(zeros, name="zeros"), ptr(bias, name="bias"),
+                            int(m), int(n), int(k), int(group_size), dt, default_stream(stream, a)),
+          "ks_gemm_w4a16")
+    return c
+
+
+def gemm_fp8_blockwise(out: TensorLike, a_fp8: TensorLike, b_fp8: TensorLike, a_scale: TensorLike,
+                       b_scale: TensorLike, m: int, n: int, k: int, block_n: int = 128, block_k: int = 128,
+                       fp8_dtype: int = None, out_dtype: int = None, stream: TensorLike = None,
+                       b_layout: str = "kn") -> TensorLike:
+    """FP8 block-scaled GEMM. ``b_layout="kn"``: ``b_fp8 [K,N]``, ``b_scale
+    [ceil(K/bk), ceil(N/bn)]`` (the reference ABI); ``b_layout="nk"``: ``b_fp8
+    [N,K]``, ``b_scale [ceil(N/bn), ceil(K/bk)]`` (checkpoint layout)."""
+    if fp8_dtype is None:
+        fp8_dtype = infer_dtype(a_fp8, None)
+    if out_dtype is None:
+        if isinstance(out, torch.Tensor):
+            out_dtype = dtype_to_ks(out.dtype)
+        else:
+            raise ValueError("out_dtype is required for ks_gemm_fp8_blockwise")
+    if b_layout not in ("kn", "nk"):
+        raise ValueError("b_layout must be 'kn' or 'nk'")
+    fn, name = ((lib.ks_gemm_fp8_blockwise, "ks_gemm_fp8_blockwise") if b_layout == "kn"
+                else (lib.ks_gemm_fp8_blockwise_nt, "ks_gemm_fp8_blockwise_nt"))
+    check(fn(ptr(out, name="out"), ptr(a_fp8, name="a_fp8"), ptr(b_fp8, name="b_fp8"),
+             f32_ptr(a_scale, name="a_scale"), f32_ptr(b_scale, name="b_scale"),
+             int(m), int(n), int(k), int(block_n), int(block_k), int(fp8_dtype), int(out_dtype),
+             default_stream(stream, out if not isinstance(out, int) else a_fp8)), name)
+    return out
