@@ -1,0 +1,369 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-GEMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One "step" is one pass of the headline workload: the DeepSeek-V3-shaped FP8
+block-scaled GEMM, A bf16 [4096, 7168] ~N(0,1) quantized in-path to e4m3 with
+1 x 128 fp32 scales, times a resident e4m3 weight [N=7168, K=7168] with
+128 x 128 fp32 block scales, bf16 output. Synthetic seeded tensors of that
+shape stand in for model weights and activations. At N > 1 the weight is split
+by N across the ranks (whole 128-column blocks, no collective) and every rank
+multiplies the full activation with its shard: total work is fixed (strong
+scaling).
+
+Rank 0 prints ONE JSON line. `value` is 2*M*N*K*steps / device time of the
+timed region (inputs resident in HBM, quantizer and GEMM both inside);
+`roofline` describes the GEMM kernel alone; `e2e` repeats the measurement with
+the activation starting in pinned host memory and the result read back;
+`cpu_baseline` is the CPU oracle of the same step timed on this machine's
+host cores. `--impl reference` prints only that CPU measurement.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M, N, K = 4096, 7168, 7168
+WORKLOAD = "fp8_blockwise_gemm M=4096 N=7168 K=7168 (A bf16 quantized in-path 1x128; W e4m3 [N,K] 128x128 scales; bf16 out)"
+ROTATE = 3  # input/output sets cycled so that no step finds its operands in L2
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    p.add_argument("--no-extras", action="store_true", help="skip the W4A16 decode sweep and CPU baseline")
+    p.add_argument("--m", type=int, default=M, help="rows of A (default: the headline 4096)")
+    return p.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_burst": float(d["bf16_tflops"]),
+                "bf16_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_inputs(m: int):
+    """Seeded CPU tensors of the headline shape; the weight is block-quantized
+    once with the oracle's statement of the reference's input preparation."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ks_oracle as orc
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(m, K, generator=g).to(torch.bfloat16)
+    w_nk = torch.randn(N, K, generator=g) * 0.02
+    # quantize_weight_blocks works on [K,N]; a transposed view gives [N,K] blocks
+    b8_kn, bs_kn = orc.quantize_weight_blocks(w_nk.t(), 128, 128)
+    return a, b8_kn.t().contiguous(), bs_kn.t().contiguous()
+
+
+def cpu_step_seconds(a, b8_nk, bs_nk, budget_s: float = 20.0):
+    """The oracle's statement of one step on the host cores: group quantizer,
+    operand dequantisation, fp32 matmul, bf16 rounding."""
+    import torch
+    import ks_oracle as orc
+
+    def step():
+        a8, a_s = orc.quantize_fp8_group(a, 128)
+        return orc.fp8_gemm_blockwise(a8, b8_nk, a_s, bs_nk, layout="nk", out_dtype=torch.bfloat16)
+
+    step()
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 10):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() > t_end and len(times) >= 2:
+            break
+    return statistics.median(times), len(times), torch.get_num_threads()
+
+
+def run_reference(args):
+    """CPU arm: the reference's torch statement of the step (restated in
+    oracle/ks_oracle.py) on this machine's host cores. Rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    a, b8, bs = make_inputs(args.m)
+    import ks_oracle as orc
+
+    def step():
+        a8, a_s = orc.quantize_fp8_group(a, 128)
+        return orc.fp8_gemm_blockwise(a8, b8, a_s, bs, layout="nk", out_dtype=torch.bfloat16)
+
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    flops = 2.0 * args.m * N * K
+    val = flops / dt / 1e12
+    threads = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": "fp8_blockwise_gemm_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "m": args.m, "n": N, "k": K},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"the whole step (quantizer + dequant + fp32 matmul), {steps} timed runs"},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def w4a16_decode_sweep(ks, torch, dev, peaks):
+    """Secondary figures: W4A16 decode shapes, achieved algorithmic GB/s."""
+    import ks_oracle as orc
+    res = []
+    for (k, n) in ((4096, 28672), (14336, 4096)):
+        g = torch.Generator().manual_seed(1)
+        copies = 3
+        bps = [torch.randint(0, 256, (k // 2, n), generator=g, dtype=torch.uint8).to(dev) for _ in range(copies)]
+        scales = (torch.randn(k // 128, n, generator=g).mul(0.02).abs() + 1e-3).to(torch.bfloat16).to(dev)
+        zeros = torch.full((k // 128, n), 8.0, dtype=torch.bfloat16, device=dev)
+        for m in (1, 8, 32, 128):
+            a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(dev)
+            c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            iters = 12
+            for i in range(3):
+                ks.gemm.gemm_w4a16(c, a, bps[i % copies], scales, zeros, m, n, k, 128)
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+            for i, (e0, e1) in enumerate(evs):
+                e0.record()
+                ks.gemm.gemm_w4a16(c, a, bps[i % copies], scales, zeros, m, n, k, 128)
+                e1.record()
+            torch.cuda.synchronize()
+            us = statistics.median(e0.elapsed_time(e1) for e0, e1 in evs) * 1e3
+            nbytes = k * n // 2 + 2 * (k // 128) * n * 2 + m * k * 2 + m * n * 2
+            gbs = nbytes / (us * 1e-6) / 1e9
+            res.append({"m": m, "k": k, "n": n, "us": round(us, 2), "gbs": round(gbs, 1),
+                        "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4),
+                        "tflops": round(2.0 * m * n * k / (us * 1e-6) / 1e12, 2)})
+        del bps
+    return res
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import kernel_set_b200 as ks
+    from kernel_set_b200 import parallel
+
+    peaks = measured_peaks()
+    m = args.m
+    a_cpu, b8_cpu, bs_cpu = make_inputs(m)
+    b8_sh, bs_sh, (n_lo, n_hi) = parallel.shard_weight_columns(b8_cpu, bs_cpu, rank, world, "nk")
+    n_local = n_hi - n_lo
+
+    # ROTATE resident copies of every operand and output (> L2 in total)
+    a_dev = [a_cpu.to(dev) for _ in range(ROTATE)]
+    b_dev = [b8_sh.to(dev) for _ in range(ROTATE)]
+    bs_dev = bs_sh.to(dev)
+    a8 = [torch.empty(m, K, dtype=torch.float8_e4m3fn, device=dev) for _ in range(ROTATE)]
+    a_s = [torch.empty(m, K // 128, dtype=torch.float32, device=dev) for _ in range(ROTATE)]
+    out = [torch.empty(m, n_local, dtype=torch.bfloat16, device=dev) for _ in range(ROTATE)]
+    a_pinned = a_cpu.pin_memory()
+    out_pinned = torch.empty(m, n_local, dtype=torch.bfloat16).pin_memory()
+
+    def quant(i):
+        ks.quant.quantize_fp8_group(a8[i], a_s[i], a_dev[i], m, K, 128)
+
+    def gemm(i):
+        ks.gemm.gemm_fp8_blockwise(out[i], a8[i], b_dev[i], a_s[i], bs_dev, m, n_local, K, b_layout="nk")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        quant(i % ROTATE)
+        gemm(i % ROTATE)
+    barrier()
+    ks.runtime.stream_synchronize(0)
+
+    # ---------------- timed region: resident inputs ----------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    gemm_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                   for _ in range(args.steps)]
+    quant_events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for s in range(args.steps):
+        i = s % ROTATE
+        quant_events[s].record()
+        quant(i)
+        gemm_events[s][0].record()
+        gemm(i)
+        gemm_events[s][1].record()
+    t_stop.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    elapsed_ms = t_start.elapsed_time(t_stop)
+    gemm_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in gemm_events)
+    quant_ms = statistics.mean(q.elapsed_time(g0) for q, (g0, _) in zip(quant_events, gemm_events))
+
+    # ---------------- end to end: host activation in, host result out ----------------
+    def e2e_step(i):
+        a_dev[i].copy_(a_pinned, non_blocking=True)
+        quant(i)
+        gemm(i)
+        out_pinned.copy_(out[i], non_blocking=True)
+
+    for i in range(2):
+        e2e_step(i % ROTATE)
+    barrier()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(3, min(args.steps, 10))
+    e_start.record()
+    for s in range(e2e_steps):
+        e2e_step(s % ROTATE)
+    e_stop.record()
+    barrier()
+    e2e_ms = e_start.elapsed_time(e_stop)
+    ks.runtime.stream_synchronize(0)
+
+    t = torch.tensor([elapsed_ms, e2e_ms, gemm_ms, quant_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms, gemm_ms, quant_ms = [float(v) for v in t.tolist()]
+
+    flops_step = 2.0 * m * N * K              # whole job, all ranks together
+    flops_gemm_rank = 2.0 * m * n_local * K   # what one GEMM launch computes
+    value = flops_step * args.steps / (elapsed_ms * 1e-3) / 1e12
+    e2e_value = flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    achieved = flops_gemm_rank / (gemm_ms * 1e-3) / 1e12
+    fp8_peak = 2.0 * peaks["bf16_sustained"]
+
+    if rank == 0:
+        line = {
+            "metric": "fp8_blockwise_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "m": m, "n": N, "k": K, "n_per_gpu": n_local,
+                       "parallelism": "single GPU" if world == 1 else f"column-parallel by N over {world} GPUs, no collective",
+                       "l2": f"rotating {ROTATE} operand/output sets per rank, larger than L2 in total"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
+                         "frac": achieved / fp8_peak, "traffic": None,
+                         "kernel": "fp8_blockwise_umma_kernel", "us_per_launch": gemm_ms * 1e3,
+                         "peak_source": f"2 x {peaks['source']} sustained cuBLAS bf16 ({peaks['bf16_sustained']} TFLOP/s); "
+                                        "no FP8 figure was measured on this pool",
+                         "frac_of_nominal_4500": achieved / 4500.0,
+                         "quantizer_us": quant_ms * 1e3,
+                         "quantizer_gbs": (m * K * 3 + m * (K // 128) * 4) / (quant_ms * 1e-3) / 1e9},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": a_pinned.numel() * 2,
+                    "d2h_bytes_per_step": out_pinned.numel() * 2, "steps": e2e_steps},
+            "gpu_launches": 2 * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_extras:
+            try:
+                line["w4a16_decode"] = w4a16_decode_sweep(ks, torch, dev, peaks)
+            except Exception as exc:  # secondary figures never take the headline down
+                line["w4a16_decode"] = f"failed: {type(exc).__name__}: {exc}"
+            sec, runs, threads = cpu_step_seconds(a_cpu, b8_cpu, bs_cpu)
+            line["cpu_baseline"] = {"value": flops_step / sec / 1e12, "unit": "TFLOP/s", "cores": threads,
+                                    "kind": "port", "seconds_per_step": sec,
+                                    "sample": f"the whole step on the host (oracle: quantizer + dequant + fp32 matmul), median of {runs} runs"}
+        print(json.dumps(line), flush=True)
+
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

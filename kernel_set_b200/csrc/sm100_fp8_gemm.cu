@@ -311,7 +311,8 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
         tmem_ld_x16(taddr, r0);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          tmem_wait_ld();
+          if (c & 1) tmem_wait_ld(r1);
+          else tmem_wait_ld(r0);
           if (c < 7) {
             if (c & 1) tmem_ld_x16(taddr + (c + 1) * 16, r0);
             else tmem_ld_x16(taddr + (c + 1) * 16, r1);

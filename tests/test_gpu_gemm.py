@@ -1,0 +1,225 @@
+"""GPU: the quantized GEMMs through the C ABI against the oracle.
+
+Acceptance (stated in the benchmark definition of this path): relative
+Frobenius error <= 1e-3 against the fp32-accumulated oracle value and
+|err| <= 2 bf16 ulp of that value per element; elements whose deviation is
+within the fp32 accumulation-order noise floor are counted separately (see
+_util.check_gemm)."""
+import os
+
+import pytest
+import torch
+
+import ks_oracle as orc
+from _util import accumulation_noise, check_gemm, fp8_inputs, from_bits16, from_u8, gen, golden, w4a16_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+class fp8_path:
+    """Pins the kernel choice of the FP8 GEMM for the duration of a block."""
+
+    def __init__(self, path=None, bn=None):
+        self.vals = {"KS_B200_FP8_PATH": path, "KS_B200_FP8_BN": str(bn) if bn else None}
+
+    def __enter__(self):
+        self.old = {k: os.environ.get(k) for k in self.vals}
+        for k, v in self.vals.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+
+    def __exit__(self, *a):
+        for k, v in self.old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+
+
+def fp8_reference(a8, a_s, b8, b_s, bn=128, bk=128):
+    ref32 = orc.fp8_gemm_blockwise(a8, b8, a_s, b_s, bn, bk, "kn", out_dtype=None)
+    a_abs = orc.dequantize_a(a8, a_s, bk).abs()
+    b_abs = orc.dequantize_b(b8, b_s, bn, bk).abs()
+    return ref32, accumulation_noise(a_abs, b_abs, a8.shape[1])
+
+
+def run_fp8(ks, dev, a8, a_s, b8_kn, b_s_kn, layout, out_dtype=torch.bfloat16, bn=128, bk=128):
+    if layout == "kn":
+        b, bs = b8_kn, b_s_kn
+    else:
+        b, bs = b8_kn.t().contiguous(), b_s_kn.t().contiguous()
+    out = ks.dispatch.fp8_gemm_blockwise(a8.to(dev), b.to(dev), a_s.to(dev), bs.to(dev), block_n=bn, block_k=bk,
+                                         out_dtype=out_dtype, b_layout=layout)
+    torch.cuda.synchronize()
+    ks.runtime.stream_synchronize(0)  # surfaces a kernel that gave up on a bounded wait
+    return out.cpu()
+
+
+@pytest.mark.parametrize("m,n,k,bn,bk,layout,out_dtype,fp8", [
+    (40, 200, 300, 128, 128, "kn", torch.float32, "e4m3"),
+    (40, 200, 300, 128, 128, "nk", torch.bfloat16, "e4m3"),
+    (65, 130, 96, 64, 32, "kn", torch.float16, "e4m3"),
+    (17, 64, 256, 128, 128, "kn", torch.bfloat16, "e5m2"),
+    (1, 48, 128, 16, 64, "nk", torch.float32, "e4m3"),
+])
+def test_fp8_general_kernel(ks, cuda, m, n, k, bn, bk, layout, out_dtype, fp8):
+    a8, a_s, b8, b_s = fp8_inputs(m, n, k, seed=m + n + k, block_n=bn, block_k=bk, fp8=fp8)
+    ref32, noise = fp8_reference(a8, a_s, b8, b_s, bn, bk)
+    with fp8_path("general"):
+        out = run_fp8(ks, cuda, a8, a_s, b8, b_s, layout, out_dtype, bn, bk)
+    ulps = 2.0 if out_dtype == torch.bfloat16 else 2.0  # f16/f32 outputs are tighter than 2 bf16 ulp
+    check_gemm(out, ref32, noise, f"general {m}x{n}x{k} {layout}", ulps=ulps)
+
+
+@pytest.mark.parametrize("m,n,k,layout,bn_tile,out_dtype,fp8", [
+    (128, 128, 128, "nk", 128, torch.float32, "e4m3"),     # one tile, one K-block
+    (128, 256, 256, "nk", 256, torch.float32, "e4m3"),
+    (128, 128, 128, "kn", 128, torch.float32, "e4m3"),     # MN-major B operand
+    (128, 256, 256, "kn", 256, torch.float32, "e4m3"),
+    (256, 512, 1024, "nk", 256, torch.bfloat16, "e4m3"),
+    (256, 512, 1024, "kn", 128, torch.bfloat16, "e4m3"),
+    (200, 336, 400, "nk", 256, torch.bfloat16, "e4m3"),    # ragged M, N, K (K % 16 == 0)
+    (200, 336, 400, "kn", 256, torch.float16, "e4m3"),
+    (77, 144, 272, "kn", 128, torch.float32, "e5m2"),
+    (1, 7168, 512, "nk", 128, torch.bfloat16, "e4m3"),     # decode-like single row
+    (1024, 2048, 7168, "nk", 256, torch.bfloat16, "e4m3"),  # several tiles per CTA, 56 K-blocks
+    (1024, 2048, 7168, "kn", 256, torch.bfloat16, "e4m3"),
+])
+def test_fp8_tcgen05_kernel(ks, cuda, m, n, k, layout, bn_tile, out_dtype, fp8):
+    a8, a_s, b8, b_s = fp8_inputs(m, n, k, seed=m * 7 + n + k, fp8=fp8)
+    ref32, noise = fp8_reference(a8, a_s, b8, b_s)
+    with fp8_path("tcgen05", bn_tile):
+        out = run_fp8(ks, cuda, a8, a_s, b8, b_s, layout, out_dtype)
+    check_gemm(out, ref32, noise, f"tcgen05 {m}x{n}x{k} {layout} bn{bn_tile}")
+    # and against the general kernel on the same inputs (fp32 out: order noise only)
+    if out_dtype == torch.float32:
+        with fp8_path("general"):
+            gen_out = run_fp8(ks, cuda, a8, a_s, b8, b_s, layout, out_dtype)
+        assert orc.rel_frobenius(out, gen_out) < 1e-5
+
+
+def test_fp8_golden(ks, cuda):
+    for tag in ("a", "b"):
+        g = golden(f"fp8_blockwise_{tag}.npz")
+        a8 = from_u8(g["a8"], torch.float8_e4m3fn)
+        b8 = from_u8(g["b8"], torch.float8_e4m3fn)
+        a_s, b_s = torch.from_numpy(g["a_scale"]), torch.from_numpy(g["b_scale"])
+        ref = torch.from_numpy(g["ref"])
+        for layout in ("kn", "nk"):
+            out = run_fp8(ks, cuda, a8, a_s, b8, b_s, layout, torch.float32)
+            assert orc.rel_frobenius(out, ref) < 1e-5, (tag, layout)
+            out16 = run_fp8(ks, cuda, a8, a_s, b8, b_s, layout, torch.bfloat16)
+            _, noise = fp8_reference(a8, a_s, b8, b_s)
+            check_gemm(out16, ref, noise, f"golden {tag} {layout}")
+
+
+@pytest.mark.parametrize("m,k,n,gs,dtype,zeros,bias", [
+    (16, 4096, 4096, 128, torch.bfloat16, True, False),   # the CPU-runnable configuration
+    (1, 256, 192, 128, torch.bfloat16, True, False),
+    (5, 128, 72, 32, torch.float16, True, True),
+    (33, 512, 100, 64, torch.bfloat16, False, True),      # zeros == NULL means zero-point 0
+    (8, 256, 64, -1, torch.float16, True, False),         # group_size <= 0: one group over K
+    (130, 384, 136, 128, torch.bfloat16, True, False),
+])
+def test_w4a16(ks, cuda, m, k, n, gs, dtype, zeros, bias):
+    a, codes, scales, zp = w4a16_inputs(m, k, n, gs, dtype, seed=m + k + n, with_zeros=zeros)
+    b_packed = orc.pack_int4_bytes(codes)
+    bias_t = torch.randn(n, generator=gen(5)).to(dtype) if bias else None
+    ref32 = orc.w4a16(a, b_packed, scales, zp, gs, bias_t, out_dtype=None)
+    w = orc.w4a16_weight(b_packed, scales, zp, gs).float()
+    noise = accumulation_noise(a.float().abs(), w.abs(), k)
+    out = ks.dispatch.w4a16(a.to(cuda), b_packed.to(cuda), scales.to(cuda), zp.to(cuda) if zp is not None else None,
+                            group_size=gs, bias=bias_t.to(cuda) if bias else None)
+    torch.cuda.synchronize()
+    assert out.dtype == dtype and out.shape == (m, n)
+    check_gemm(out.cpu(), ref32, noise, f"w4a16 {m}x{n}x{k}")
+
+
+def test_w4a16_golden(ks, cuda):
+    for tag, dt in (("bf16", torch.bfloat16), ("f16", torch.float16)):
+        g = golden(f"w4a16_{tag}.npz")
+        a = from_bits16(g["a"], dt)
+        bp = torch.from_numpy(g["b_packed"])
+        sc, zp = from_bits16(g["scales"], dt), from_bits16(g["zeros"], dt)
+        gs = int(g["group_size"])
+        out = ks.dispatch.w4a16(a.to(cuda), bp.to(cuda), sc.to(cuda), zp.to(cuda), group_size=gs).cpu()
+        ref = from_bits16(g["out"], dt).float()
+        ref32 = orc.w4a16(a, bp, sc, zp, gs, out_dtype=None)
+        # the frozen output is the rounded reference; ours may differ from it by one rounding step
+        check_gemm(out, ref32, accumulation_noise(a.float().abs(), orc.w4a16_weight(bp, sc, zp, gs).float().abs(),
+                                                  a.shape[1]), f"w4a16 golden {tag}")
+        assert orc.rel_frobenius(out.float(), ref) < 2e-3
+
+
+def ragged_offsets(rows_per_expert):
+    off = [0]
+    for r in rows_per_expert:
+        off.append(off[-1] + r)
+    return torch.tensor(off, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_grouped_gemm_plain(ks, cuda, dtype):
+    offs = ragged_offsets([5, 0, 70, 1, 64, 0])
+    total, k, n, e = int(offs[-1]), 96, 80, 6
+    g = gen(9)
+    a = torch.randn(total, k, generator=g).to(dtype)
+    b = torch.randn(e, k, n, generator=g).to(dtype)
+    out = ks.dispatch.moe(a.to(cuda), b.to(cuda), offs.to(cuda), num_experts=e, n=n, k=k)
+    torch.cuda.synchronize()
+    ref32 = orc.grouped_gemm(a, b, offs.tolist(), out_dtype=None)
+    assert orc.rel_frobenius(out.cpu().float(), ref32) < (1e-6 if dtype == torch.float32 else 3e-3)
+    if dtype == torch.bfloat16:
+        g2 = golden("grouped_gemm_bf16.npz")
+        a2, b2 = from_bits16(g2["a"], dtype), from_bits16(g2["b"], dtype)
+        o2 = torch.from_numpy(g2["offsets"])
+        out2 = ks.dispatch.moe(a2.to(cuda), b2.to(cuda), o2.to(cuda), num_experts=b2.shape[0], n=b2.shape[2],
+                               k=b2.shape[1]).cpu()
+        assert orc.rel_frobenius(out2.float(), from_bits16(g2["out"], dtype).float()) < 3e-3
+
+
+def test_grouped_gemm_plain_fp8_operands(ks, cuda):
+    """fp8 dtype: raw code values multiplied, C written in the same fp8 type."""
+    offs = ragged_offsets([3, 20])
+    g = gen(4)
+    a = torch.randn(23, 32, generator=g).to(torch.float8_e4m3fn)
+    b = (torch.randn(2, 32, 16, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    out = ks.dispatch.moe(a.to(cuda), b.to(cuda), offs.to(cuda), num_experts=2, n=16, k=32).cpu()
+    ref = orc.grouped_gemm(a, b, offs.tolist(), out_dtype=None).clamp(-448, 448).to(torch.float8_e4m3fn)
+    assert (out.float() - ref.float()).abs().max() <= 0.13 * ref.float().abs().max()
+
+
+@pytest.mark.parametrize("layout,path,n,k", [
+    ("nk", "general", 200, 300),
+    ("kn", "general", 200, 300),
+    ("nk", "tcgen05", 512, 384),
+    ("kn", "tcgen05", 512, 384),
+    ("nk", "tcgen05", 336, 400),
+])
+def test_grouped_gemm_fp8_blockwise(ks, cuda, layout, path, n, k):
+    rows = [130, 0, 7, 256, 1, 129, 0, 64]
+    e = len(rows)
+    offs = ragged_offsets(rows)
+    total = int(offs[-1])
+    g = gen(n + k)
+    a = torch.randn(total, k, generator=g).to(torch.bfloat16)
+    a8, a_s = orc.quantize_fp8_group(a, 128)
+    b8_l, bs_l = [], []
+    for _ in range(e):
+        w_kn = torch.randn(k, n, generator=g) * 0.02
+        b8, bs = orc.quantize_weight_blocks(w_kn, 128, 128)
+        if layout == "nk":
+            b8, bs = b8.t().contiguous(), bs.t().contiguous()
+        b8_l.append(b8)
+        bs_l.append(bs)
+    b8, bs = torch.stack(b8_l), torch.stack(bs_l)
+    ref32 = orc.grouped_gemm_fp8_blockwise(a8, b8, a_s, bs, offs.tolist(), layout=layout, out_dtype=None)
+    with fp8_path(path):
+        out = ks.dispatch.moe(a8.to(cuda), b8.to(cuda), offs.to(cuda), num_experts=e, n=n, k=k, a_scale=a_s.to(cuda),
+                              b_scale=bs.to(cuda), b_layout=layout)
+        torch.cuda.synchronize()
+        ks.runtime.stream_synchronize(0)
+    noise = torch.full_like(ref32, float(ref32.abs().max()) * 1e-5)
+    check_gemm(out.cpu(), ref32, noise, f"grouped fp8 {layout} {path}")
