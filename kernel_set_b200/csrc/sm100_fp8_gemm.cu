@@ -12,10 +12,15 @@
 //               128-byte swizzle, completion counted on the stage's `full` barrier
 //   warp 1      MMA issuer: 4 UMMAs (M128, N=BN, K32) per K-block into TMEM buffer
 //               kb & 1; tcgen05.commit releases the stage and publishes the partial
-//   warps 2..   epilogue: warp w reads TMEM lanes 32*(w%4).. and 128 columns,
+//   warps 2,3   idle (they complete warpgroup 0 so that register budgets can be
+//               moved between warpgroups with setmaxnreg)
+//   warps 4..   epilogue: warp w reads TMEM lanes 32*(w%4).. and 128 columns in
+//               32-column loads, double-buffered so that one load is in flight
+//               while the previous one is folded in:
 //               acc = fma(partial, a_scale[row,kb] * b_scale[kb,nb], acc) in
-//               registers, frees the TMEM buffer, and after the last K-block
-//               rounds once to the output type and stores its row segment
+//               registers (packed two-wide), frees the TMEM buffer, and after
+//               the last K-block rounds once to the output type and stores its
+//               row segment
 // B may be stored [N,K] (K-major UMMA operand) or [K,N] (MN-major operand, the
 // layout of the reference C ABI); both are loaded by TMA without a transpose.
 //
@@ -42,7 +47,11 @@ struct Cfg {
   static constexpr int kBBytes = BN * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kEpiWarps = (BN / 128) * 4;
-  static constexpr int kThreads = 64 + kEpiWarps * 32;
+  static constexpr int kThreads = 128 + kEpiWarps * 32;
+  // With 12 warps the launch-time budget is 168 registers per thread; the
+  // epilogue needs 128 accumulators + 64 in-flight TMEM values, so warpgroup 0
+  // gives registers up and the epilogue warpgroups take them.
+  static constexpr bool kRebalanceRegs = (BN == 256);
   static constexpr int kTmemCols = 2 * BN;
   // ring + 1024 B alignment slack + barriers/flags + grouped tile prefix and offsets
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + 2 * 4 * (kMaxExperts + 1);
@@ -210,6 +219,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
+    if constexpr (C::kRebalanceRegs) setmaxnreg_dec<40>();
     uint32_t it = 0;
     bool ok = true;
     TileCoord tc;
@@ -237,6 +247,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
+    if constexpr (C::kRebalanceRegs) setmaxnreg_dec<40>();
     uint32_t it = 0;
     bool ok = true;
     TileCoord tc;
@@ -270,10 +281,11 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
         __syncwarp();
       }
     }
-  } else {
+  } else if (warp >= 4) {
     // -------------------------------- epilogue --------------------------------
+    if constexpr (C::kRebalanceRegs) setmaxnreg_inc<232>();
     const int quarter = warp & 3;         // TMEM lane quarter this warp can address
-    const int half = (warp - 2) >> 2;     // 128-column half of the tile
+    const int half = (warp - 4) >> 2;     // 128-column half of the tile
     const int row_in_tile = quarter * 32 + lane;
     OutT* out = static_cast<OutT*>(p.out);
     uint32_t it = 0;
@@ -290,14 +302,15 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
                             (NT ? static_cast<size_t>(nb) * p.nkb : static_cast<size_t>(nb));
       const size_t bs_step = NT ? 1 : static_cast<size_t>(p.nnb);
 
-      float acc[128];
+      float2 acc[64];
 #pragma unroll
-      for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+      for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.f, 0.f);
       float as_next = row_ok ? __ldg(as_ptr) : 0.f;
       float bs_next = __ldg(bs_ptr);
 
       for (int kb = 0; kb < p.nkb; ++kb, ++it) {
         const float scale = as_next * bs_next;
+        const float2 scale2 = make_float2(scale, scale);
         if (kb + 1 < p.nkb) {
           as_next = row_ok ? __ldg(as_ptr + kb + 1) : 0.f;
           bs_next = __ldg(bs_ptr + static_cast<size_t>(kb + 1) * bs_step);
@@ -307,15 +320,15 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
         if (!mbar_wait(wctx, bar_tfull + 8 * buf, aph, 0x400u + buf)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + half * 128;
-        uint32_t r0[16], r1[16];
-        tmem_ld_x16(taddr, r0);
+        uint32_t r0[32], r1[32];
+        tmem_ld_x32(taddr, r0);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
           if (c & 1) tmem_wait_ld(r1);
           else tmem_wait_ld(r0);
-          if (c < 7) {
-            if (c & 1) tmem_ld_x16(taddr + (c + 1) * 16, r0);
-            else tmem_ld_x16(taddr + (c + 1) * 16, r1);
+          if (c < 3) {
+            if (c & 1) tmem_ld_x32(taddr + (c + 1) * 32, r0);
+            else tmem_ld_x32(taddr + (c + 1) * 32, r1);
           } else {
             // every column of this warp's slice is in registers: hand the buffer back
             tc_fence_before_sync();
@@ -324,8 +337,9 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float v = __uint_as_float((c & 1) ? r1[j] : r0[j]);
-            acc[c * 16 + j] = fmaf(v, scale, acc[c * 16 + j]);
+            const float lo = __uint_as_float((c & 1) ? r1[2 * j] : r0[2 * j]);
+            const float hi = __uint_as_float((c & 1) ? r1[2 * j + 1] : r0[2 * j + 1]);
+            ffma2(acc[c * 16 + j], lo, hi, scale2);
           }
         }
       }
@@ -334,10 +348,19 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const int valid = p.n - (col0 + c * 16);
-          if (valid > 0) store_16<OutT>(dst + c * 16, &acc[c * 16], p.vec_store != 0, valid);
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[2 * j] = acc[c * 8 + j].x;
+            v[2 * j + 1] = acc[c * 8 + j].y;
+          }
+          if (valid > 0) store_16<OutT>(dst + c * 16, v, p.vec_store != 0, valid);
         }
       }
     }
+  } else {
+    // warps 2 and 3 only complete warpgroup 0
+    if constexpr (C::kRebalanceRegs) setmaxnreg_dec<40>();
   }
 
   // ------------------------------- teardown -------------------------------
