@@ -36,6 +36,10 @@ namespace ksb {
 namespace sm100 {
 namespace {
 
+#ifndef KSB_FP8_EPI_CHUNK
+#define KSB_FP8_EPI_CHUNK 16
+#endif
+
 constexpr int kBM = 128;
 constexpr int kBK = 128;
 constexpr int kMaxExperts = 1024;
@@ -305,41 +309,60 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
       float2 acc[64];
 #pragma unroll
       for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.f, 0.f);
-      float as_next = row_ok ? __ldg(as_ptr) : 0.f;
-      float bs_next = __ldg(bs_ptr);
 
-      for (int kb = 0; kb < p.nkb; ++kb, ++it) {
-        const float scale = as_next * bs_next;
-        const float2 scale2 = make_float2(scale, scale);
-        if (kb + 1 < p.nkb) {
-          as_next = row_ok ? __ldg(as_ptr + kb + 1) : 0.f;
-          bs_next = __ldg(bs_ptr + static_cast<size_t>(kb + 1) * bs_step);
+      // Scales are fetched two K-blocks at a time, one group ahead of use: an
+      // L2 round trip is longer than one K-block, so a load issued for the next
+      // block alone would sit on the critical path.
+      constexpr int G = 2;
+      constexpr int CW = KSB_FP8_EPI_CHUNK;  // TMEM columns per load
+      float as_nxt[G], bs_nxt[G];
+      auto fetch_scales = [&](int kb0) {
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+          const int kb = kb0 + j;
+          const bool in = kb < p.nkb;
+          as_nxt[j] = (in && row_ok) ? __ldg(as_ptr + kb) : 0.f;
+          bs_nxt[j] = in ? __ldg(bs_ptr + static_cast<size_t>(kb) * bs_step) : 0.f;
         }
-        const uint32_t buf = it & 1u;
-        const uint32_t aph = (it >> 1) & 1u;
-        if (!mbar_wait(wctx, bar_tfull + 8 * buf, aph, 0x400u + buf)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + half * 128;
-        uint32_t r0[32], r1[32];
-        tmem_ld_x32(taddr, r0);
+      };
+      fetch_scales(0);
+
+      for (int kb0 = 0; kb0 < p.nkb && ok; kb0 += G) {
+        float sc[G];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          if (c & 1) tmem_wait_ld(r1);
-          else tmem_wait_ld(r0);
-          if (c < 3) {
-            if (c & 1) tmem_ld_x32(taddr + (c + 1) * 32, r0);
-            else tmem_ld_x32(taddr + (c + 1) * 32, r1);
-          } else {
-            // every column of this warp's slice is in registers: hand the buffer back
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
-          }
+        for (int j = 0; j < G; ++j) sc[j] = as_nxt[j] * bs_nxt[j];
+        fetch_scales(kb0 + G);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float lo = __uint_as_float((c & 1) ? r1[2 * j] : r0[2 * j]);
-            const float hi = __uint_as_float((c & 1) ? r1[2 * j + 1] : r0[2 * j + 1]);
-            ffma2(acc[c * 16 + j], lo, hi, scale2);
+        for (int j4 = 0; j4 < G; ++j4) {
+          if (kb0 + j4 >= p.nkb) break;
+          const float2 scale2 = make_float2(sc[j4], sc[j4]);
+          const uint32_t buf = it & 1u;
+          const uint32_t aph = (it >> 1) & 1u;
+          ++it;
+          if (!mbar_wait(wctx, bar_tfull + 8 * buf, aph, 0x400u + buf)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + half * 128;
+          uint32_t r0[CW], r1[CW];
+          tmem_ld(taddr, r0);
+#pragma unroll
+          for (int c = 0; c < 128 / CW; ++c) {
+            if (c & 1) tmem_wait_ld(r1);
+            else tmem_wait_ld(r0);
+            if (c < 128 / CW - 1) {
+              if (c & 1) tmem_ld(taddr + (c + 1) * CW, r0);
+              else tmem_ld(taddr + (c + 1) * CW, r1);
+            } else {
+              // every column of this warp's slice is in registers: hand the buffer back
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+            }
+#pragma unroll
+            for (int j = 0; j < CW / 2; ++j) {
+              const float lo = __uint_as_float((c & 1) ? r1[2 * j] : r0[2 * j]);
+              const float hi = __uint_as_float((c & 1) ? r1[2 * j + 1] : r0[2 * j + 1]);
+              ffma2(acc[c * (CW / 2) + j], lo, hi, scale2);
+            }
           }
         }
       }

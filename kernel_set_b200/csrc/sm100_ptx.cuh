@@ -67,11 +67,18 @@ struct WaitCtx {
 // another waiter of this CTA has already given up or when this one times out;
 // `code` identifies the wait site in the recorded fault word.
 __device__ __forceinline__ bool mbar_wait(const WaitCtx& ctx, uint32_t bar, uint32_t parity, uint32_t code) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // Fast path: plain polling, no timer and no shared-memory traffic besides the
+  // barrier itself. Each failed try_wait may itself block for a short,
+  // hardware-defined time, so this phase already covers every healthy wait.
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  // Slow path: something upstream is late. Keep polling, but watch the clock
+  // and the CTA's abort flag.
   const unsigned long long t0 = global_ns();
   while (true) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*ctx.abort_flag != 0u) return false;
     if (global_ns() - t0 > kWaitLimitNs) {
@@ -146,7 +153,7 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[16]) {
 }
 // Lane i of the warp receives 16 consecutive fp32 columns of TMEM lane
 // (taddr.lane + i). A warp may only address the 32-lane quarter warp_id % 4.
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -157,7 +164,7 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 
 // 32-column variant: lane i receives columns [col, col+32) of its TMEM lane.
-__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
