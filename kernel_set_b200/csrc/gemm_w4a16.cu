@@ -3,7 +3,10 @@
 // choice.
 #include "common.cuh"
 #include "gemm_general.cuh"
+#include <cstdlib>
+
 #include "kernel_set/gemm.h"
+#include "sm100_w4a16.cuh"
 
 extern "C" ks_status_t ks_gemm_w4a16(void* c, const void* a, const void* b_packed, const void* scales,
                                      const void* zeros, const void* bias, int64_t m, int64_t n, int64_t k,
@@ -26,11 +29,22 @@ extern "C" ks_status_t ks_gemm_w4a16(void* c, const void* a, const void* b_packe
   if (st != KS_SUCCESS) return st;
   st = poll_kernel_fault(where);
   if (st != KS_SUCCESS) return st;
+  cudaStream_t s = as_stream(stream);
+  {
+    // KS_B200_W4A16_PATH=general pins the general kernel, =tcgen05 refuses to
+    // fall back; unset means "choose" (tests and profiling only).
+    const char* env = std::getenv("KS_B200_W4A16_PATH");
+    const int path = env == nullptr ? 0 : (env[0] == 'g' ? 1 : (env[0] == 't' ? 2 : 0));
+    sm100::W4A16Args args;
+    args.c = c; args.a = a; args.b_packed = b_packed; args.scales = scales; args.zeros = zeros; args.bias = bias;
+    args.m = m; args.n = n; args.k = k; args.group_size = gs; args.dtype = dtype;
+    if (path != 1 && sm100::w4a16_eligible(args)) return sm100::launch_w4a16(args, s);
+    if (path == 2) KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE, "ks_gemm_w4a16: shape not eligible for the tcgen05 kernel");
+  }
   const int64_t tiles_m = (m + general::kTM - 1) / general::kTM;
   const int64_t tiles_n = (n + general::kTN - 1) / general::kTN;
   if (tiles_m > 2147483647LL || tiles_n > 65535LL)
     KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE, "ks_gemm_w4a16: tile grid exceeds CUDA grid limits");
-  cudaStream_t s = as_stream(stream);
   dim3 grid(static_cast<unsigned>(tiles_m), static_cast<unsigned>(tiles_n));
   if (dtype == KS_DTYPE_F16) {
     general::w4a16_kernel<__half><<<grid, general::kThreads, 0, s>>>(

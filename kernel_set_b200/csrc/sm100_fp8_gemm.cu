@@ -30,12 +30,16 @@
 
 #include "common.cuh"
 #include "sm100_fp8_gemm.cuh"
+#include "sm100_host.cuh"
 #include "sm100_ptx.cuh"
 
 namespace ksb {
 namespace sm100 {
 namespace {
 
+#ifndef KSB_FP8_EPI_COLS
+#define KSB_FP8_EPI_COLS 128
+#endif
 #ifndef KSB_FP8_EPI_CHUNK
 #define KSB_FP8_EPI_CHUNK 16
 #endif
@@ -50,12 +54,21 @@ struct Cfg {
   static constexpr int kABytes = kBM * kBK;
   static constexpr int kBBytes = BN * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kEpiWarps = (BN / 128) * 4;
+  // An epilogue warp owns 32 TMEM lanes x kEpiCols columns. Narrow slices keep
+  // the per-K-block chain (wait, TMEM loads, FMAs, release) short: with 64
+  // columns it is ~440 cycles, under the ~512 the MMAs of a K-block take.
+  static constexpr int kEpiCols = KSB_FP8_EPI_COLS;
+  static constexpr int kEpiWarps = (BN / kEpiCols) * 4;
   static constexpr int kThreads = 128 + kEpiWarps * 32;
-  // With 12 warps the launch-time budget is 168 registers per thread; the
-  // epilogue needs 128 accumulators + 64 in-flight TMEM values, so warpgroup 0
-  // gives registers up and the epilogue warpgroups take them.
+  // Warpgroup 0 (TMA, MMA issue) hands registers to the epilogue warpgroups,
+  // which hold the accumulators plus the TMEM values in flight. The budgets must add up to no more than
+  // the CTA's launch-time pool (threads x launch registers): setmaxnreg.inc
+  // blocks, without a time limit, until the pool can satisfy it.
   static constexpr bool kRebalanceRegs = (BN == 256);
+  // 64-column slices: 20 warps, 96 registers at launch -> 32 / 112.
+  // 128-column slices: 12 warps, 168 registers at launch -> 40 / 232.
+  static constexpr int kRegsIssue = kEpiCols == 64 ? 32 : 40;
+  static constexpr int kRegsEpi = kEpiCols == 64 ? 112 : 232;
   static constexpr int kTmemCols = 2 * BN;
   // ring + 1024 B alignment slack + barriers/flags + grouped tile prefix and offsets
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + 2 * 4 * (kMaxExperts + 1);
@@ -161,6 +174,10 @@ __device__ __forceinline__ void store_16<__half>(__half* dst, const float* v, bo
   }
 }
 
+static_assert(128 * Cfg<256>::kRegsIssue + (Cfg<256>::kThreads - 128) * Cfg<256>::kRegsEpi <=
+                  Cfg<256>::kThreads * ((65536 / Cfg<256>::kThreads) & ~7),
+              "setmaxnreg budgets exceed the register pool the CTA is launched with");
+
 template <int BN, bool NT, bool GROUPED, typename OutT>
 __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
 fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -223,7 +240,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if constexpr (C::kRebalanceRegs) setmaxnreg_dec<40>();
+    if constexpr (C::kRebalanceRegs) setmaxnreg_dec<C::kRegsIssue>();
     uint32_t it = 0;
     bool ok = true;
     TileCoord tc;
@@ -232,26 +249,25 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
         const uint32_t s = it % C::kStages;
         const uint32_t ph = (it / C::kStages) & 1u;
         if (!mbar_wait(wctx, bar_empty + 8 * s, ph ^ 1u, 0x100u + s)) { ok = false; break; }
-        if (lane == 0) {
+        {
           const uint32_t full = bar_full + 8 * s;
           const uint32_t a_dst = ring + s * C::kStageBytes;
           const uint32_t b_dst = a_dst + C::kABytes;
-          mbar_arrive_expect_tx(full, C::kStageBytes);
-          tma_load_2d(a_dst, &tm_a, full, kb * kBK, tc.row0);
+          mbar_arrive_expect_tx_elect(full, C::kStageBytes);
+          tma_load_2d_elect(a_dst, &tm_a, full, kb * kBK, tc.row0);
           if constexpr (NT) {
-            tma_load_3d(b_dst, &tm_b, full, kb * kBK, tc.n0, tc.expert);
+            tma_load_3d_elect(b_dst, &tm_b, full, kb * kBK, tc.n0, tc.expert);
           } else {
 #pragma unroll
             for (int h = 0; h < BN / 128; ++h)
-              tma_load_3d(b_dst + h * (128 * kBK), &tm_b, full, tc.n0 + h * 128, kb * kBK, tc.expert);
+              tma_load_3d_elect(b_dst + h * (128 * kBK), &tm_b, full, tc.n0 + h * 128, kb * kBK, tc.expert);
           }
         }
-        __syncwarp();
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if constexpr (C::kRebalanceRegs) setmaxnreg_dec<40>();
+    if constexpr (C::kRebalanceRegs) setmaxnreg_dec<C::kRegsIssue>();
     uint32_t it = 0;
     bool ok = true;
     TileCoord tc;
@@ -264,7 +280,8 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
         if (!mbar_wait(wctx, bar_tempty + 8 * buf, aph ^ 1u, 0x200u + buf)) { ok = false; break; }
         if (!mbar_wait(wctx, bar_full + 8 * s, ph, 0x300u + s)) { ok = false; break; }
         tc_fence_after_sync();
-        if (lane == 0) {
+        {
+          // all 32 lanes run this code; each instruction elects its one issuing lane
           const uint32_t a_src = ring + s * C::kStageBytes;
           const uint32_t b_src = a_src + C::kABytes;
           const uint32_t d_tmem = tmem_base + buf * BN;
@@ -277,19 +294,19 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
             const uint64_t a_desc = umma_smem_desc_sw128(a_src + kk * 32, 16, 1024);
             const uint64_t b_desc = NT ? umma_smem_desc_sw128(b_src + kk * 32, 16, 1024)
                                        : umma_smem_desc_sw128(b_src + kk * 32 * 128, 128 * kBK, 1024);
-            umma_f8f6f4(d_tmem, a_desc, b_desc, p.idesc, kk > 0 ? 1u : 0u);
+            umma_f8f6f4_elect(d_tmem, a_desc, b_desc, p.idesc, kk > 0 ? 1u : 0u);
           }
-          tc_commit(bar_empty + 8 * s);
-          tc_commit(bar_tfull + 8 * buf);
+          tc_commit_elect(bar_empty + 8 * s);
+          tc_commit_elect(bar_tfull + 8 * buf);
         }
-        __syncwarp();
       }
     }
   } else if (warp >= 4) {
     // -------------------------------- epilogue --------------------------------
-    if constexpr (C::kRebalanceRegs) setmaxnreg_inc<232>();
+    if constexpr (C::kRebalanceRegs) setmaxnreg_inc<C::kRegsEpi>();
     const int quarter = warp & 3;         // TMEM lane quarter this warp can address
-    const int half = (warp - 4) >> 2;     // 128-column half of the tile
+    const int slice = (warp - 4) >> 2;    // which kEpiCols-wide column slice of the tile
+    constexpr int EC = C::kEpiCols;
     const int row_in_tile = quarter * 32 + lane;
     OutT* out = static_cast<OutT*>(p.out);
     uint32_t it = 0;
@@ -298,7 +315,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     for (int t = blockIdx.x; ok && locate_tile<BN, GROUPED>(p, prefix, offs, t, &tc); t += gridDim.x) {
       const int row = tc.row0 + row_in_tile;
       const bool row_ok = row < tc.row_end;
-      const int col0 = tc.n0 + half * 128;
+      const int col0 = tc.n0 + slice * EC;
       int nb = col0 >> 7;
       if (nb > p.nnb - 1) nb = p.nnb - 1;
       const float* as_ptr = p.a_scale + static_cast<size_t>(row_ok ? row : 0) * p.nkb;
@@ -306,9 +323,9 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
                             (NT ? static_cast<size_t>(nb) * p.nkb : static_cast<size_t>(nb));
       const size_t bs_step = NT ? 1 : static_cast<size_t>(p.nnb);
 
-      float2 acc[64];
+      float2 acc[EC / 2];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.f, 0.f);
+      for (int i = 0; i < EC / 2; ++i) acc[i] = make_float2(0.f, 0.f);
 
       // Scales are fetched two K-blocks at a time, one group ahead of use: an
       // L2 round trip is longer than one K-block, so a load issued for the next
@@ -341,14 +358,14 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
           ++it;
           if (!mbar_wait(wctx, bar_tfull + 8 * buf, aph, 0x400u + buf)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + half * 128;
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + slice * EC;
           uint32_t r0[CW], r1[CW];
           tmem_ld(taddr, r0);
 #pragma unroll
-          for (int c = 0; c < 128 / CW; ++c) {
+          for (int c = 0; c < EC / CW; ++c) {
             if (c & 1) tmem_wait_ld(r1);
             else tmem_wait_ld(r0);
-            if (c < 128 / CW - 1) {
+            if (c < EC / CW - 1) {
               if (c & 1) tmem_ld(taddr + (c + 1) * CW, r0);
               else tmem_ld(taddr + (c + 1) * CW, r1);
             } else {
@@ -369,7 +386,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
       if (ok && row_ok) {
         OutT* dst = out + static_cast<size_t>(row) * p.n + col0;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < EC / 16; ++c) {
           const int valid = p.n - (col0 + c * 16);
           float v[16];
 #pragma unroll
@@ -383,7 +400,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     }
   } else {
     // warps 2 and 3 only complete warpgroup 0
-    if constexpr (C::kRebalanceRegs) setmaxnreg_dec<40>();
+    if constexpr (C::kRebalanceRegs) setmaxnreg_dec<C::kRegsIssue>();
   }
 
   // ------------------------------- teardown -------------------------------
@@ -402,39 +419,11 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
 }
 
 // ------------------------------- host side --------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-    cudaGetLastError();
-  });
-  return fn;
-}
-
 // Byte tensor of rank 2 or 3 (innermost first), 128-byte swizzled boxes.
 bool encode_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                const uint32_t* box) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return false;
-  cuuint64_t gdim[3];
-  cuuint64_t gstr[2];
-  cuuint32_t bdim[3];
-  cuuint32_t estr[3] = {1, 1, 1};
-  for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bdim[i] = box[i]; }
-  for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
-                        gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  return tma_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, base, dims, strides_bytes, box,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 template <int BN, bool NT, bool GROUPED, typename OutT>
@@ -487,7 +476,7 @@ bool fp8_blockwise_eligible(const Fp8GemmArgs& a) {
   if (!aligned16(a.a) || !aligned16(a.b)) return false;
   if (a.m > INT32_MAX / 2 || a.n > INT32_MAX / 2 || a.k > INT32_MAX / 2) return false;
   if (a.offsets != nullptr && (a.num_experts > kMaxExperts || a.num_experts < 1)) return false;
-  return encode_fn() != nullptr;
+  return tma_available();
 }
 
 ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {

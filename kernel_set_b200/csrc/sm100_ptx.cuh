@@ -26,6 +26,22 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 
+// True in exactly one lane of a converged warp. Code guarded by it is known to
+// the compiler to run in a single thread, which lets tcgen05 / TMA operands
+// travel in uniform registers instead of through a per-lane fallback loop.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 rx;\n\t"
+      ".reg .pred px;\n\t"
+      "elect.sync rx|px, 0xFFFFFFFF;\n\t"
+      "selp.u32 %0, 1, 0, px;\n\t"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- mbarrier ---------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -197,14 +213,24 @@ __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
-// Two fp32 fused multiply-adds in one instruction: acc = a * b + acc, per half.
+// acc = a * b + acc on two fp32 lanes. KSB_FFMA2=1 uses the packed
+// fma.rn.f32x2 instruction (operands travel as 64-bit register pairs);
+// KSB_FFMA2=0 issues two scalar FMAs.
+#ifndef KSB_FFMA2
+#define KSB_FFMA2 1
+#endif
 __device__ __forceinline__ void ffma2(float2& acc, float a_lo, float a_hi, float2 b) {
+#if KSB_FFMA2
   uint64_t d, a, bb;
   asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(acc.x), "f"(acc.y));
   asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a_lo), "f"(a_hi));
   asm("mov.b64 %0, {%1, %2};" : "=l"(bb) : "f"(b.x), "f"(b.y));
   asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(bb));
   asm("mov.b64 {%0, %1}, %2;" : "=f"(acc.x), "=f"(acc.y) : "l"(d));
+#else
+  acc.x = fmaf(a_lo, b.x, acc.x);
+  acc.y = fmaf(a_hi, b.y, acc.y);
+#endif
 }
 
 // ---- UMMA descriptors --------------------------------------------------------------
@@ -254,6 +280,63 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       "}\n" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+
+// ---- single-lane issue from converged code -----------------------------------------
+// The *_elect wrappers below are called by all 32 lanes of a converged warp;
+// elect.sync picks one lane and the instruction is predicated on it inside the
+// same asm statement. Issued this way a tcgen05.mma costs ~55 cycles; issued
+// from inside an `if (lane == 0)` branch it measured ~160 cycles, which made
+// instruction issue, not the tensor pipe, the bound. Successive elections in a
+// converged warp pick the same lane, so a commit tracks the MMAs before it.
+#define KSB_ELECT_PROLOGUE ".reg .pred q;\n\t.reg .b32 rx;\n\telect.sync rx|q, 0xFFFFFFFF;\n\t"
+
+__device__ __forceinline__ void umma_f8f6f4_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t" KSB_ELECT_PROLOGUE
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+__device__ __forceinline__ void umma_f16_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t" KSB_ELECT_PROLOGUE
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+__device__ __forceinline__ void tc_commit_elect(uint32_t bar) {
+  asm volatile("{\n\t" KSB_ELECT_PROLOGUE
+               "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_elect(uint32_t bar, uint32_t bytes) {
+  asm volatile("{\n\t" KSB_ELECT_PROLOGUE
+               "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}\n" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_elect(uint32_t bar) {
+  asm volatile("{\n\t" KSB_ELECT_PROLOGUE "@q mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}\n" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_elect(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar, int x,
+                                                  int y) {
+  asm volatile("{\n\t" KSB_ELECT_PROLOGUE
+               "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+               "[%2];\n\t}\n" ::"r"(smem_dst),
+               "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_elect(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar, int x, int y,
+                                                  int z) {
+  asm volatile("{\n\t" KSB_ELECT_PROLOGUE
+               "@q cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, "
+               "%5}], [%2];\n\t}\n" ::"r"(smem_dst),
+               "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+               : "memory");
 }
 
 }  // namespace sm100

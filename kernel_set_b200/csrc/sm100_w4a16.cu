@@ -1,0 +1,582 @@
+// int4 weight-only GEMM for sm_100a, built for the decode regime (few
+// activation rows, the packed weight read once from HBM).
+//
+// Computes what ks_gemm_w4a16 declares (reference: kernels/src/gemm/
+// gemm_w4a16.cu:50-130, layout :6-19): C[M,N] = A[M,K] . W + bias with
+// W[k,n] = (q[k,n] - zero[g,n]) * scale[g,n] rounded once to the activation
+// type (the reference's torch statement, benchmarks/bench.py:1275-1284), then
+// multiplied with fp32 accumulation.
+//
+// The GEMM is transposed onto the tensor core: the weight's N dimension is the
+// UMMA M dimension (128 TMEM lanes), the tokens are the UMMA N dimension
+// (16..128 columns), so a CTA streams 128 weight columns x 128 k per step:
+//   warp 0        weight producer (TMA): packed tile [64 byte-rows x 128 columns]
+//                 = 8 KB straight from HBM plus the group's 128 scales and
+//                 zero-points (2 x 256 B), ten stages deep
+//   warp 2        activation producer (TMA): the K-slice [tokens x 128] (from L2)
+//   warps 4-11    dequantisation: 8 packed bytes -> 16 weights per step:
+//                 nibble -> (128 + q) by byte-permute into a bf16 pattern,
+//                 minus (128 + zero), times scale, two packed 16-bit ops;
+//                 written as the MN-major, 128-byte-swizzled UMMA A operand
+//   warp 1        MMA issuer: 8 x tcgen05.mma kind::f16 (M128, N=tokens, K16)
+//                 per step into a TMEM accumulator
+//   warps 12-15   epilogue: TMEM -> registers -> C, or -> an fp32 partial slot
+//   warp 3        idle
+// Work is cut stream-K style: the (column tile, K-step) units are dealt to the
+// CTAs in equal contiguous runs, so every SM streams the same number of bytes
+// whatever N is. A column tile whose K range is shared by several CTAs is
+// finished by the last CTA to arrive: each writes its fp32 partial to its own
+// slot, bumps the tile's counter, and the one that completes the count sums the
+// slots in slot order (deterministic) and writes C. Slots and counters live in
+// library-owned scratch memory that stays in L2.
+//
+// Roofline: HBM-bound for M <= 64; algorithmic bytes per launch
+// K*N/2 + (K/gs)*N*2*(1 or 2) + M*K*2 + M*N*2.
+#include <mutex>
+
+#include "common.cuh"
+#include "sm100_host.cuh"
+#include "sm100_ptx.cuh"
+#include "sm100_w4a16.cuh"
+
+namespace ksb {
+namespace sm100 {
+namespace {
+
+constexpr int kTileN = 128;    // weight columns per tile = UMMA M
+constexpr int kStepK = 128;    // k per pipeline step (one scale group when gs % 128 == 0)
+constexpr int kRawBytes = (kStepK / 2) * kTileN;      // 8192
+constexpr int kRawStage = kRawBytes + 2 * 256;        // + scales + zeros of the step
+constexpr int kDeqBytes = kStepK * kTileN * 2;        // 32768: dequantised UMMA operand
+constexpr int kThreads = 512;
+constexpr int kDeqWarps = 8;
+
+template <int MTMAX>
+struct Cfg {
+  static constexpr int kRawStages = MTMAX <= 32 ? 9 : 6;
+  static constexpr int kActStages = MTMAX <= 32 ? 4 : 3;
+  static constexpr int kDeqStages = MTMAX <= 32 ? 3 : 2;
+  // Consecutive K=16 instructions of a step go to different TMEM accumulators:
+  // an instruction that accumulates into the result of the previous one waits
+  // for it, and with 16..32 token columns that latency, not throughput, would
+  // set the pace. The epilogue adds the accumulators up.
+  static constexpr int kAccs = MTMAX <= 32 ? 8 : 2;
+  static constexpr int kTmemCols = 2 * kAccs * MTMAX;  // two segment buffers
+  static constexpr int kActStage = MTMAX * kStepK * 2;  // bytes reserved per activation stage
+  static constexpr int kRing = kDeqStages * kDeqBytes + kActStages * kActStage + kRawStages * kRawStage;
+  static constexpr int kNumBars = 2 * kRawStages + 2 * kActStages + 2 * kDeqStages + 4;
+  static constexpr int kSmemBytes = kRing + 1024 + 512;
+};
+
+struct Params {
+  void* c;
+  const void* bias;
+  float* slots;             // [tiles][max_parts][mt][128] fp32 partials
+  unsigned int* counters;   // [tiles]
+  unsigned int* fault_word;
+  int m, n, k;
+  int mt;                   // token tile, multiple of 16, <= MTMAX
+  int m_tiles;
+  int n_tiles, k_steps;
+  int gs_steps;             // K-steps per scale group (group_size / 128)
+  int max_parts;
+  int has_zeros;
+  uint32_t idesc;
+};
+
+// Units (tile * k_steps + step) are dealt in equal contiguous runs.
+__device__ __forceinline__ long long run_start(long long units, int ctas, int c) {
+  return (units * c) / ctas;
+}
+__device__ __forceinline__ int cta_of_unit(long long units, int ctas, long long u) {
+  int c = static_cast<int>((u * ctas) / units);
+  while (c + 1 < ctas && run_start(units, ctas, c + 1) <= u) ++c;
+  while (c > 0 && run_start(units, ctas, c) > u) --c;
+  return c;
+}
+
+template <typename T> struct Pack16;
+template <> struct Pack16<__nv_bfloat16> {
+  using V2 = __nv_bfloat162;
+  static constexpr uint32_t kMagicBytes = 0x43434343u;  // high byte of bf16(128 + q)
+  static constexpr float kMagic = 128.0f;
+  static constexpr float kMaxZero = 127.0f;
+  __device__ static V2 from_bits(uint32_t b) { return *reinterpret_cast<V2*>(&b); }
+  __device__ static uint32_t bits(V2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+  __device__ static V2 splat(float f) { return __float2bfloat162_rn(f); }
+  __device__ static float lo(V2 v) { return __low2float(v); }
+  __device__ static float hi(V2 v) { return __high2float(v); }
+  __device__ static V2 make(float a, float b) { return __floats2bfloat162_rn(a, b); }
+};
+template <> struct Pack16<__half> {
+  using V2 = __half2;
+  static constexpr uint32_t kMagicBytes = 0x64646464u;  // high byte of f16(1024 + q)
+  static constexpr float kMagic = 1024.0f;
+  static constexpr float kMaxZero = 1023.0f;
+  __device__ static V2 from_bits(uint32_t b) { return *reinterpret_cast<V2*>(&b); }
+  __device__ static uint32_t bits(V2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+  __device__ static V2 splat(float f) { return __float2half2_rn(f); }
+  __device__ static float lo(V2 v) { return __low2float(v); }
+  __device__ static float hi(V2 v) { return __high2float(v); }
+  __device__ static V2 make(float a, float b) { return __floats2half2_rn(a, b); }
+};
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+template <typename T, int MTMAX>
+__global__ void __launch_bounds__(kThreads, 1)
+w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
+                  const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_a,
+                  const Params p) {
+  using C = Cfg<MTMAX>;
+  using P16 = Pack16<T>;
+  using V2 = typename P16::V2;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw_addr);
+  // ring: dequantised operand stages | activation stages | raw stages | barriers
+  const uint32_t deq_base = base;
+  const uint32_t act_base = deq_base + C::kDeqStages * kDeqBytes;
+  const uint32_t rawst_base = act_base + C::kActStages * C::kActStage;
+  const uint32_t bar_base = rawst_base + C::kRawStages * kRawStage;
+  uint8_t* deq_ptr = base_ptr;
+  uint8_t* rawst_ptr = base_ptr + (rawst_base - base);
+  uint8_t* ctrl_ptr = base_ptr + (bar_base - base);
+  const uint32_t bar_raw_full = bar_base;
+  const uint32_t bar_raw_empty = bar_raw_full + 8 * C::kRawStages;
+  const uint32_t bar_act_full = bar_raw_empty + 8 * C::kRawStages;
+  const uint32_t bar_act_empty = bar_act_full + 8 * C::kActStages;
+  const uint32_t bar_deq_full = bar_act_empty + 8 * C::kActStages;
+  const uint32_t bar_deq_empty = bar_deq_full + 8 * C::kDeqStages;
+  const uint32_t bar_acc_full = bar_deq_empty + 8 * C::kDeqStages;
+  const uint32_t bar_acc_empty = bar_acc_full + 16;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl_ptr + 8 * C::kNumBars);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* last_flag = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const WaitCtx wctx{abort_flag, p.fault_word};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kRawStages; ++s) {
+      mbar_init(bar_raw_full + 8 * s, 1);
+      mbar_init(bar_raw_empty + 8 * s, kDeqWarps);
+    }
+    for (int s = 0; s < C::kActStages; ++s) {
+      mbar_init(bar_act_full + 8 * s, 1);
+      mbar_init(bar_act_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < C::kDeqStages; ++s) {
+      mbar_init(bar_deq_full + 8 * s, kDeqWarps);
+      mbar_init(bar_deq_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, 4);
+    }
+    *abort_flag = 0u;
+    fence_barrier_init();
+    prefetch_tensormap(&tm_w);
+    prefetch_tensormap(&tm_s);
+    prefetch_tensormap(&tm_a);
+    if (p.has_zeros) prefetch_tensormap(&tm_z);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Unit space: (token tile, column tile, K-step), K-step fastest. With one
+  // token tile the units are dealt in exact equal runs (column tiles may be
+  // split between CTAs); with several, runs are snapped to whole column tiles
+  // so that no partial sums arise.
+  const long long units = static_cast<long long>(p.n_tiles) * p.k_steps;   // per token tile
+  const int ctas = gridDim.x;
+  long long u_begin, u_end;
+  if (p.m_tiles == 1) {
+    u_begin = run_start(units, ctas, blockIdx.x);
+    u_end = run_start(units, ctas, blockIdx.x + 1);
+  } else {
+    const long long tiles_total = static_cast<long long>(p.m_tiles) * p.n_tiles;
+    u_begin = run_start(tiles_total, ctas, blockIdx.x) * p.k_steps;
+    u_end = run_start(tiles_total, ctas, blockIdx.x + 1) * p.k_steps;
+  }
+  const uint32_t act_tx = static_cast<uint32_t>(p.mt) * kStepK * 2;
+  const uint32_t raw_tx = kRawBytes + 256 + (p.has_zeros ? 256 : 0);
+
+  if (warp == 0) {
+    // ------------------------- weight producer (TMA) -------------------------
+    uint32_t it = 0;
+    for (long long u = u_begin; u < u_end; ++u, ++it) {
+      const long long ul = u % units;
+      const int tile = static_cast<int>(ul / p.k_steps);
+      const int step = static_cast<int>(ul - static_cast<long long>(tile) * p.k_steps);
+      const uint32_t sr = it % C::kRawStages, pr = (it / C::kRawStages) & 1u;
+      if (!mbar_wait(wctx, bar_raw_empty + 8 * sr, pr ^ 1u, 0x100u + sr)) break;
+      {
+        const uint32_t full = bar_raw_full + 8 * sr;
+        const uint32_t dst = rawst_base + sr * kRawStage;
+        mbar_arrive_expect_tx_elect(full, raw_tx);
+        tma_load_2d_elect(dst, &tm_w, full, tile * kTileN, step * (kStepK / 2));
+        tma_load_2d_elect(dst + kRawBytes, &tm_s, full, tile * kTileN, step / p.gs_steps);
+        if (p.has_zeros) tma_load_2d_elect(dst + kRawBytes + 256, &tm_z, full, tile * kTileN, step / p.gs_steps);
+      }
+    }
+  } else if (warp == 2) {
+    // ----------------------- activation producer (TMA) -----------------------
+    uint32_t it = 0;
+    for (long long u = u_begin; u < u_end; ++u, ++it) {
+      const int mtile = static_cast<int>(u / units);
+      const long long ul = u - static_cast<long long>(mtile) * units;
+      const int step = static_cast<int>(ul % p.k_steps);
+      const uint32_t sa = it % C::kActStages, pa = (it / C::kActStages) & 1u;
+      if (!mbar_wait(wctx, bar_act_empty + 8 * sa, pa ^ 1u, 0x180u + sa)) break;
+      {
+        const uint32_t full = bar_act_full + 8 * sa;
+        const uint32_t dst = act_base + sa * C::kActStage;
+        mbar_arrive_expect_tx_elect(full, act_tx);
+        tma_load_2d_elect(dst, &tm_a, full, step * kStepK, mtile * p.mt);
+        tma_load_2d_elect(dst + p.mt * 128, &tm_a, full, step * kStepK + 64, mtile * p.mt);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    uint32_t it = 0, seg = 0;
+    {
+      int step = static_cast<int>(u_begin % p.k_steps);
+      for (long long u = u_begin; u < u_end; ++u, ++it, step = (step + 1 == p.k_steps) ? 0 : step + 1) {
+        const bool seg_first = (u == u_begin) || (step == 0);
+        const bool seg_last = (u + 1 == u_end) || (step == p.k_steps - 1);
+        const uint32_t sd = it % C::kDeqStages, pd = (it / C::kDeqStages) & 1u;
+        const uint32_t sa = it % C::kActStages, pa = (it / C::kActStages) & 1u;
+        const uint32_t buf = seg & 1u, pacc = (seg >> 1) & 1u;
+        if (seg_first && !mbar_wait(wctx, bar_acc_empty + 8 * buf, pacc ^ 1u, 0x200u + buf)) break;
+        if (!mbar_wait(wctx, bar_deq_full + 8 * sd, pd, 0x280u + sd)) break;
+        if (!mbar_wait(wctx, bar_act_full + 8 * sa, pa, 0x300u + sa)) break;
+        tc_fence_after_sync();
+        {
+          // all 32 lanes run this code; each instruction elects its one issuing lane
+          const uint32_t w_src = deq_base + sd * kDeqBytes;
+          const uint32_t a_src = act_base + sa * C::kActStage;
+          const uint32_t d_tmem = tmem_base + buf * (C::kAccs * MTMAX);
+#pragma unroll
+          for (int kk = 0; kk < kStepK / 16; ++kk) {
+            // Weights: MN-major, 64-column atoms 16 KB apart, 8-k groups 1024 B
+            // apart, 16 k = 2048 B per instruction. Tokens: K-major, two 64-k
+            // atoms of mt rows, 32 B per instruction inside an atom.
+            const uint64_t w_desc = umma_smem_desc_sw128(w_src + kk * 2048, 16384, 1024);
+            const uint64_t a_desc = umma_smem_desc_sw128(a_src + (kk >> 2) * (p.mt * 128) + (kk & 3) * 32, 16, 1024);
+            umma_f16_elect(d_tmem + (kk % C::kAccs) * MTMAX, w_desc, a_desc, p.idesc,
+                           (seg_first && kk < C::kAccs) ? 0u : 1u);
+          }
+          tc_commit_elect(bar_deq_empty + 8 * sd);
+          tc_commit_elect(bar_act_empty + 8 * sa);
+          if (seg_last) tc_commit_elect(bar_acc_full + 8 * buf);
+        }
+        if (seg_last) ++seg;
+      }
+    }
+  } else if (warp >= 4 && warp < 4 + kDeqWarps) {
+    // ----------------------------- dequantisation -----------------------------
+    const int tt = threadIdx.x - 128;
+    const int oct = tt & 15;   // 8 weight columns: n_local = 8*oct .. 8*oct+7
+    const int rg = tt >> 4;    // 4 packed byte-rows: k_local = 8*rg .. 8*rg+7
+    const uint32_t atom_off = (oct >> 3) * 16384u;
+    const uint32_t chunk = oct & 7;
+    uint32_t it = 0;
+    {
+      for (long long u = u_begin; u < u_end; ++u, ++it) {
+        const uint32_t sr = it % C::kRawStages, pr = (it / C::kRawStages) & 1u;
+        const uint32_t sd = it % C::kDeqStages, pd = (it / C::kDeqStages) & 1u;
+        if (!mbar_wait(wctx, bar_raw_full + 8 * sr, pr, 0x400u + sr)) break;
+        const uint8_t* raw = rawst_ptr + sr * kRawStage;
+        // group constants of this thread's 8 columns
+        const uint4 s4 = *reinterpret_cast<const uint4*>(raw + kRawBytes + oct * 16);
+        uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+        if (p.has_zeros) z4 = *reinterpret_cast<const uint4*>(raw + kRawBytes + 256 + oct * 16);
+        const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
+        const uint32_t zw[4] = {z4.x, z4.y, z4.z, z4.w};
+        V2 sc[4], zz[4];
+        bool simple = true;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          sc[j] = P16::from_bits(sw[j]);
+          const V2 z = P16::from_bits(zw[j]);
+          const float z0 = P16::lo(z), z1 = P16::hi(z);
+          simple = simple && (z0 == rintf(z0)) && (z1 == rintf(z1)) && z0 >= 0.f && z1 >= 0.f &&
+                   z0 <= P16::kMaxZero && z1 <= P16::kMaxZero;
+          zz[j] = P16::make(z0 + P16::kMagic, z1 + P16::kMagic);  // exact for integer zero-points
+        }
+        uint2 pk[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pk[i] = *reinterpret_cast<const uint2*>(raw + (rg * 4 + i) * kTileN + oct * 8);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_raw_empty + 8 * sr);  // the packed stage is in registers
+        if (!mbar_wait(wctx, bar_deq_empty + 8 * sd, pd ^ 1u, 0x480u + sd)) break;
+        uint8_t* deq = deq_ptr + sd * kDeqBytes + atom_off;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r_even = rg * 8 + 2 * i;
+          uint32_t even[4], odd[4];
+          if (simple) {
+            const uint32_t words[2] = {pk[i].x, pk[i].y};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint32_t e = words[h] & 0x0F0F0F0Fu;
+              const uint32_t o = (words[h] >> 4) & 0x0F0F0F0Fu;
+              // bytes (q0,q1,q2,q3) -> 16-bit patterns magic|q for (q0,q1) and (q2,q3)
+              const V2 e01 = P16::from_bits(__byte_perm(e, P16::kMagicBytes, 0x4140));
+              const V2 e23 = P16::from_bits(__byte_perm(e, P16::kMagicBytes, 0x4342));
+              const V2 o01 = P16::from_bits(__byte_perm(o, P16::kMagicBytes, 0x4140));
+              const V2 o23 = P16::from_bits(__byte_perm(o, P16::kMagicBytes, 0x4342));
+              even[2 * h] = P16::bits(__hmul2(__hsub2(e01, zz[2 * h]), sc[2 * h]));
+              even[2 * h + 1] = P16::bits(__hmul2(__hsub2(e23, zz[2 * h + 1]), sc[2 * h + 1]));
+              odd[2 * h] = P16::bits(__hmul2(__hsub2(o01, zz[2 * h]), sc[2 * h]));
+              odd[2 * h + 1] = P16::bits(__hmul2(__hsub2(o23, zz[2 * h + 1]), sc[2 * h + 1]));
+            }
+          } else {
+            // zero-points that are not small integers: the fp32 statement, verbatim
+            const uint64_t w64 = (static_cast<uint64_t>(pk[i].y) << 32) | pk[i].x;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const V2 z = P16::from_bits(zw[j]);
+              const float z0 = P16::lo(z), z1 = P16::hi(z);
+              const float s0 = P16::lo(sc[j]), s1 = P16::hi(sc[j]);
+              const uint32_t b0 = static_cast<uint32_t>(w64 >> (16 * j)) & 0xFFu;
+              const uint32_t b1 = static_cast<uint32_t>(w64 >> (16 * j + 8)) & 0xFFu;
+              even[j] = P16::bits(P16::make(__fmul_rn(__fsub_rn(static_cast<float>(b0 & 15u), z0), s0),
+                                            __fmul_rn(__fsub_rn(static_cast<float>(b1 & 15u), z1), s1)));
+              odd[j] = P16::bits(P16::make(__fmul_rn(__fsub_rn(static_cast<float>(b0 >> 4), z0), s0),
+                                           __fmul_rn(__fsub_rn(static_cast<float>(b1 >> 4), z1), s1)));
+            }
+          }
+          // rows r_even and r_even+1 of the operand: 128 B per 64 columns, 16-byte
+          // chunks xor-swizzled with the row index inside each group of 8 rows
+          *reinterpret_cast<uint4*>(deq + r_even * 128 + ((chunk ^ (r_even & 7)) << 4)) =
+              make_uint4(even[0], even[1], even[2], even[3]);
+          *reinterpret_cast<uint4*>(deq + (r_even + 1) * 128 + ((chunk ^ ((r_even + 1) & 7)) << 4)) =
+              make_uint4(odd[0], odd[1], odd[2], odd[3]);
+        }
+        fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_deq_full + 8 * sd);
+      }
+    }
+  } else if (warp >= 12) {
+    // -------------------------------- epilogue --------------------------------
+    const int quarter = warp & 3;
+    const int n_local = quarter * 32 + lane;   // TMEM lane = weight column inside the tile
+    const int et = threadIdx.x - 384;
+    T* c = static_cast<T*>(p.c);
+    const T* bias = static_cast<const T*>(p.bias);
+    uint32_t seg = 0;
+    {
+      long long u = u_begin;
+      while (u < u_end) {
+        const int mtile = static_cast<int>(u / units);
+        const int m0 = mtile * p.mt;
+        const long long ul = u - static_cast<long long>(mtile) * units;
+        const int tile = static_cast<int>(ul / p.k_steps);
+        const int step0 = static_cast<int>(ul - static_cast<long long>(tile) * p.k_steps);
+        const long long tile_end = u - step0 + p.k_steps;
+        const long long seg_end = tile_end < u_end ? tile_end : u_end;
+        const bool whole = (step0 == 0) && (seg_end == tile_end);
+        const uint32_t buf = seg & 1u, pacc = (seg >> 1) & 1u;
+        ++seg;
+        u = seg_end;
+        if (!mbar_wait(wctx, bar_acc_full + 8 * buf, pacc, 0x500u + buf)) break;
+        tc_fence_after_sync();
+        const int n = tile * kTileN + n_local;
+        const bool n_ok = n < p.n;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * (C::kAccs * MTMAX);
+        // which slot of the tile this CTA's segment is
+        // (only reached with a single token tile, where u indexes `units` directly)
+        const int first_cta = whole ? 0 : cta_of_unit(units, ctas, static_cast<long long>(tile) * p.k_steps);
+        const int last_cta = whole ? 0 : cta_of_unit(units, ctas, tile_end - 1);
+        const int parts = last_cta - first_cta + 1;
+        const int part = static_cast<int>(blockIdx.x) - first_cta;
+        float* slot = p.slots + (static_cast<size_t>(tile) * p.max_parts + part) * (static_cast<size_t>(p.mt) * kTileN);
+        const float bias_v = (whole && bias != nullptr && n_ok) ? to_f32<T>(bias[n]) : 0.f;
+        for (int cc = 0; cc < p.mt; cc += 16) {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+#pragma unroll
+          for (int acc = 0; acc < C::kAccs; ++acc) {
+            uint32_t r[16];
+            tmem_ld(taddr + acc * MTMAX + cc, r);
+            tmem_wait_ld(r);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(r[j]);
+          }
+          if (whole) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + cc + j;
+              if (m < p.m && n_ok) c[static_cast<size_t>(m) * p.n + n] = from_f32<T>(v[j] + bias_v);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) slot[(cc + j) * kTileN + n_local] = v[j];
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+        if (!whole) {
+          // publish the partial, then find out whether this CTA completes the tile
+          __threadfence();
+          named_barrier_sync(1, 128);
+          if (et == 0) {
+            const unsigned int prev = atomicAdd(p.counters + tile, 1u);
+            *last_flag = (prev == static_cast<unsigned int>(parts - 1)) ? 1u : 0u;
+            if (prev == static_cast<unsigned int>(parts - 1)) p.counters[tile] = 0u;  // ready for the next launch
+          }
+          named_barrier_sync(1, 128);
+          if (*last_flag != 0u) {
+            __threadfence();
+            const float* tile_slots = p.slots + static_cast<size_t>(tile) * p.max_parts * (static_cast<size_t>(p.mt) * kTileN);
+            const float bv = (bias != nullptr && n_ok) ? to_f32<T>(bias[n]) : 0.f;
+            for (int mm = 0; mm < p.mt; ++mm) {
+              const int m = m0 + mm;
+              if (m >= p.m) break;
+              float sum = 0.f;
+              for (int q = 0; q < parts; ++q)
+                sum += __ldcg(tile_slots + (static_cast<size_t>(q) * p.mt + mm) * kTileN + n_local);
+              if (n_ok) c[static_cast<size_t>(m) * p.n + n] = from_f32<T>(sum + bv);
+            }
+          }
+          named_barrier_sync(1, 128);  // last_flag may be rewritten only after everyone has read it
+        }
+      }
+    }
+  }
+
+  // ------------------------------- teardown -------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <typename T, int MTMAX>
+ks_status_t launch_t(const W4A16Args& a, const CUtensorMap& tm_w, const CUtensorMap& tm_s, const CUtensorMap& tm_z,
+                     const CUtensorMap& tm_a, const Params& p, int grid, cudaStream_t stream) {
+  using C = Cfg<MTMAX>;
+  auto kernel = w4a16_umma_kernel<T, MTMAX>;
+  static std::mutex mu;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+      if (e != cudaSuccess) return cuda_status(e, "ks_gemm_w4a16");
+      attr_done[dev] = true;
+    }
+  }
+  kernel<<<grid, kThreads, C::kSmemBytes, stream>>>(tm_w, tm_s, tm_z, tm_a, p);
+  return cuda_status(cudaGetLastError(), "ks_gemm_w4a16");
+}
+
+}  // namespace
+
+bool w4a16_eligible(const W4A16Args& a) {
+  if (a.k % kStepK != 0) return false;
+  if (a.group_size % kStepK != 0) return false;   // one scale row per 128-k step
+  if (a.n % 16 != 0) return false;                // 16-byte row pitch of the packed weight and of the scales
+  if (!aligned16(a.a) || !aligned16(a.b_packed) || !aligned16(a.scales)) return false;
+  if (a.zeros != nullptr && !aligned16(a.zeros)) return false;
+  if (a.m > (1 << 24) || a.n > (1 << 28) || a.k > (1 << 28)) return false;
+  return tma_available();
+}
+
+ks_status_t launch_w4a16(const W4A16Args& a, cudaStream_t stream) {
+  const bool bf16 = a.dtype == KS_DTYPE_BF16;
+  const int mt_raw = static_cast<int>(a.m < 128 ? a.m : 128);
+  const int mt = (mt_raw + 15) & ~15;
+  const int mtmax = mt <= 32 ? 32 : 128;
+  const int n_tiles = static_cast<int>((a.n + kTileN - 1) / kTileN);
+  const int k_steps = static_cast<int>(a.k / kStepK);
+  const long long units = static_cast<long long>(n_tiles) * k_steps;
+  const int sms = sm_count();
+  const int grid = static_cast<int>(units < sms ? units : sms);
+  const long long per_cta = units / grid;  // shortest run
+  const int max_parts = static_cast<int>((k_steps + per_cta - 1) / per_cta) + 1;
+
+  const size_t slot_bytes = static_cast<size_t>(n_tiles) * max_parts * mt * kTileN * sizeof(float);
+  const size_t counter_bytes = (static_cast<size_t>(n_tiles) * sizeof(unsigned int) + 255) & ~size_t(255);
+  uint8_t* scratch = static_cast<uint8_t*>(stream_scratch(stream, counter_bytes + slot_bytes));
+  if (scratch == nullptr) KSB_FAIL(KS_ERROR_OUT_OF_MEMORY, "ks_gemm_w4a16: workspace allocation failed");
+
+  const CUtensorMapDataType dt16 = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap tm_w, tm_s, tm_z, tm_a;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k / 2)};
+    const uint64_t str[1] = {static_cast<uint64_t>(a.n)};
+    const uint32_t box[2] = {static_cast<uint32_t>(kTileN), static_cast<uint32_t>(kStepK / 2)};
+    if (!tma_encode(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.b_packed, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+      KSB_FAIL(KS_ERROR_INTERNAL, "ks_gemm_w4a16: tensor map for the packed weight rejected");
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k / a.group_size)};
+    const uint64_t str[1] = {static_cast<uint64_t>(a.n) * 2};
+    const uint32_t box[2] = {static_cast<uint32_t>(kTileN), 1u};
+    if (!tma_encode(&tm_s, dt16, 2, a.scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+      KSB_FAIL(KS_ERROR_INTERNAL, "ks_gemm_w4a16: tensor map for the scales rejected");
+    if (!tma_encode(&tm_z, dt16, 2, a.zeros != nullptr ? a.zeros : a.scales, dims, str, box,
+                    CU_TENSOR_MAP_SWIZZLE_NONE))
+      KSB_FAIL(KS_ERROR_INTERNAL, "ks_gemm_w4a16: tensor map for the zero-points rejected");
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.m)};
+    const uint64_t str[1] = {static_cast<uint64_t>(a.k) * 2};
+    const uint32_t box[2] = {64u, static_cast<uint32_t>(mt)};
+    if (!tma_encode(&tm_a, dt16, 2, a.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      KSB_FAIL(KS_ERROR_INTERNAL, "ks_gemm_w4a16: tensor map for the activations rejected");
+  }
+
+  Params p;
+  p.c = a.c;
+  p.bias = a.bias;
+  p.counters = reinterpret_cast<unsigned int*>(scratch);
+  p.slots = reinterpret_cast<float*>(scratch + counter_bytes);
+  p.fault_word = kernel_fault_word();
+  p.m = static_cast<int>(a.m);
+  p.n = static_cast<int>(a.n);
+  p.k = static_cast<int>(a.k);
+  p.mt = mt;
+  p.m_tiles = static_cast<int>((a.m + mt - 1) / mt);
+  p.n_tiles = n_tiles;
+  p.k_steps = k_steps;
+  p.gs_steps = a.group_size / kStepK;
+  p.max_parts = max_parts;
+  p.has_zeros = a.zeros != nullptr ? 1 : 0;
+  const uint32_t fmt = bf16 ? 1u : 0u;
+  p.idesc = umma_instr_desc(fmt, fmt, 1u, 0u, 128u, static_cast<uint32_t>(mt));
+
+  if (bf16) {
+    return mtmax == 32 ? launch_t<__nv_bfloat16, 32>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream)
+                       : launch_t<__nv_bfloat16, 128>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream);
+  }
+  return mtmax == 32 ? launch_t<__half, 32>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream)
+                     : launch_t<__half, 128>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream);
+}
+
+}  // namespace sm100
+}  // namespace ksb

@@ -137,6 +137,74 @@ def test_w4a16(ks, cuda, m, k, n, gs, dtype, zeros, bias):
     check_gemm(out.cpu(), ref32, noise, f"w4a16 {m}x{n}x{k}")
 
 
+class w4_path:
+    def __init__(self, path):
+        self.path = path
+
+    def __enter__(self):
+        self.old = os.environ.get("KS_B200_W4A16_PATH")
+        os.environ["KS_B200_W4A16_PATH"] = self.path
+
+    def __exit__(self, *a):
+        if self.old is None:
+            os.environ.pop("KS_B200_W4A16_PATH", None)
+        else:
+            os.environ["KS_B200_W4A16_PATH"] = self.old
+
+
+@pytest.mark.parametrize("m,k,n,gs,dtype,zeros,bias", [
+    (1, 128, 128, 128, torch.bfloat16, "eight", False),      # one unit
+    (16, 256, 128, 128, torch.bfloat16, "eight", False),
+    (16, 128, 256, 128, torch.bfloat16, "eight", False),
+    (8, 4096, 256, 128, torch.bfloat16, "eight", True),      # each column tile split over 32 CTAs
+    (32, 1024, 2048, 128, torch.bfloat16, "random", False),  # integer zero-points 0..15
+    (32, 1024, 2048, 256, torch.float16, "random", True),    # two K-steps per scale group
+    (5, 512, 208, 128, torch.bfloat16, None, False),         # ragged last column tile, zeros == NULL
+    (128, 512, 384, 128, torch.bfloat16, "eight", False),    # full token tile
+    (77, 384, 512, 128, torch.float16, "fraction", False),   # non-integer zero-points: exact fp32 path
+    (300, 256, 640, 128, torch.bfloat16, "eight", True),     # several token tiles
+    (32, 4096, 28672 // 8, 128, torch.bfloat16, "eight", False),
+])
+def test_w4a16_tcgen05(ks, cuda, m, k, n, gs, dtype, zeros, bias):
+    g = gen(m + k + n)
+    a = torch.randn(m, k, generator=g).to(dtype)
+    codes = torch.randint(0, 16, (k, n), generator=g).to(torch.int32)
+    scales = (torch.randn(k // gs, n, generator=g).mul(0.02).abs() + 1e-3).to(dtype)
+    if zeros == "eight":
+        zp = torch.full((k // gs, n), 8.0).to(dtype)
+    elif zeros == "random":
+        zp = torch.randint(0, 16, (k // gs, n), generator=g).to(dtype)
+    elif zeros == "fraction":
+        zp = (torch.rand(k // gs, n, generator=g) * 15).to(dtype)
+    else:
+        zp = None
+    b_packed = orc.pack_int4_bytes(codes)
+    bias_t = torch.randn(n, generator=g).to(dtype) if bias else None
+    ref32 = orc.w4a16(a, b_packed, scales, zp, gs, bias_t, out_dtype=None)
+    w = orc.w4a16_weight(b_packed, scales, zp, gs).float()
+    noise = accumulation_noise(a.float().abs(), w.abs(), k)
+    with w4_path("tcgen05"):
+        out = ks.dispatch.w4a16(a.to(cuda), b_packed.to(cuda), scales.to(cuda),
+                                zp.to(cuda) if zp is not None else None, group_size=gs,
+                                bias=bias_t.to(cuda) if bias else None)
+        torch.cuda.synchronize()
+        ks.runtime.stream_synchronize(0)
+        # a second call reuses the scratch memory (counters must have reset themselves)
+        out2 = ks.dispatch.w4a16(a.to(cuda), b_packed.to(cuda), scales.to(cuda),
+                                 zp.to(cuda) if zp is not None else None, group_size=gs,
+                                 bias=bias_t.to(cuda) if bias else None)
+        torch.cuda.synchronize()
+    check_gemm(out.cpu(), ref32, noise, f"w4a16 tcgen05 {m}x{n}x{k}")
+    assert torch.equal(out.cpu().view(torch.int16), out2.cpu().view(torch.int16)), "not reproducible run to run"
+    with w4_path("general"):
+        gen_out = ks.dispatch.w4a16(a.to(cuda), b_packed.to(cuda), scales.to(cuda),
+                                    zp.to(cuda) if zp is not None else None, group_size=gs,
+                                    bias=bias_t.to(cuda) if bias else None)
+        torch.cuda.synchronize()
+    # both kernels multiply the same rounded weights; they differ by summation order only
+    assert orc.rel_frobenius(out.cpu().float(), gen_out.cpu().float()) < 2e-3
+
+
 def test_w4a16_golden(ks, cuda):
     for tag, dt in (("bf16", torch.bfloat16), ("f16", torch.float16)):
         g = golden(f"w4a16_{tag}.npz")
