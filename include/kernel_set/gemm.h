@@ -42,6 +42,44 @@ KS_API ks_status_t ks_gemm_w4a16(void* c, const void* a, const void* b_packed,
                                  ks_stream_t stream);
 
 /*
+ * ks_gemm_w4a16 for callers that are not allowed to allocate. It has no
+ * counterpart in the reference project.
+ *
+ * The fast kernel behind ks_gemm_w4a16 splits K between thread blocks and
+ * needs a few MiB of device scratch for the partial sums; ks_gemm_w4a16
+ * obtains it from the stream-ordered CUDA allocator the first time a stream
+ * is used. Some hosts cannot tolerate that: an inference server that hands
+ * the whole GPU to its own pool at start-up (a later cudaMalloc inside a
+ * plugin then fails or stalls), a latency-critical decode loop that bans
+ * allocator calls once it is running, a sandbox that only lets a plugin
+ * launch kernels and copy memory. This entry point performs the same
+ * computation with the scratch in a fixed 16 MiB array that is part of the
+ * library image (KS_W4A16_STATIC_SCRATCH_BYTES; every GPU that loads the
+ * library carries it until the process exits) and calls neither cudaMalloc /
+ * cudaFree nor any other allocating routine.
+ *
+ * Arguments, results and status codes are those of ks_gemm_w4a16, plus:
+ *  - a shape whose scratch need exceeds the array (roughly: more than 128
+ *    weight-column tiles x 32 token rows x 8 K-splits) is refused with
+ *    KS_ERROR_UNSUPPORTED_SHAPE and a message naming both sizes;
+ *  - the first call on each device resolves the array's device address; make
+ *    that call before starting any stream capture;
+ *  - all calls on a device share the one array, so two calls whose kernels
+ *    may overlap on the GPU (different streams, no ordering between them)
+ *    race on it. Calls on one stream, or ordered by events, are safe.
+ */
+#define KS_W4A16_STATIC_SCRATCH_BYTES (16u << 20)
+KS_API ks_status_t ks_gemm_w4a16_static_scratch(void* c, const void* a,
+                                                const void* b_packed,
+                                                const void* scales,
+                                                const void* zeros,
+                                                const void* bias, int64_t m,
+                                                int64_t n, int64_t k,
+                                                int group_size,
+                                                ks_dtype_t dtype,
+                                                ks_stream_t stream);
+
+/*
  * out[m,n] = sum over K-blocks kb of
  *            a_scale[m,kb] * b_scale[kb, n/block_n] * sum_{k in kb} A8[m,k]*B8[k,n]
  * with the inner sum and the outer sum both kept in fp32.

@@ -156,7 +156,9 @@ _decl("ks_memcpy", [_VP, _VP, c_size_t, c_int, _VP])
 _decl("ks_memset_device", [_VP, c_int, c_size_t, _VP])
 
 # gemm.h
-_decl("ks_gemm_w4a16", [_VP, _VP, _VP, _VP, _VP, _VP, c_int64, c_int64, c_int64, c_int, c_int, _VP])
+_W4A16 = [_VP, _VP, _VP, _VP, _VP, _VP, c_int64, c_int64, c_int64, c_int, c_int, _VP]
+_decl("ks_gemm_w4a16", _W4A16)
+_decl("ks_gemm_w4a16_static_scratch", _W4A16)
 _FP8_BW = [_VP, _VP, _VP, POINTER(c_float), POINTER(c_float), c_int64, c_int64, c_int64,
            c_int, c_int, c_int, c_int, _VP]
 _decl("ks_gemm_fp8_blockwise", _FP8_BW)

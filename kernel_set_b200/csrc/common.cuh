@@ -38,6 +38,9 @@ int sm_count();
 ks_status_t poll_kernel_fault(const char* where);
 // Device-visible address of that word for the current device (NULL on failure).
 unsigned int* kernel_fault_word();
+// The same address if an earlier call already set the word up, else NULL.
+// Never allocates (the set-up in kernel_fault_word() pins a host page).
+unsigned int* kernel_fault_word_if_ready();
 
 inline cudaStream_t as_stream(ks_stream_t s) {
   return static_cast<cudaStream_t>(s);

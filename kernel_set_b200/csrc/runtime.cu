@@ -90,6 +90,13 @@ unsigned int* kernel_fault_word() {
   return d->fault_dev;
 }
 
+unsigned int* kernel_fault_word_if_ready() {
+  DeviceInfo* d = current_device_info();
+  if (d == nullptr) return nullptr;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  return d->fault_dev;
+}
+
 ks_status_t poll_kernel_fault(const char* where) {
   DeviceInfo* d = current_device_info();
   if (d == nullptr || d->fault_host == nullptr) return KS_SUCCESS;

@@ -32,6 +32,7 @@
 //
 // Roofline: HBM-bound for M <= 64; algorithmic bytes per launch
 // K*N/2 + (K/gs)*N*2*(1 or 2) + M*K*2 + M*N*2.
+#include <cstdio>
 #include <mutex>
 
 #include "common.cuh"
@@ -506,24 +507,38 @@ bool w4a16_eligible(const W4A16Args& a) {
   return tma_available();
 }
 
-ks_status_t launch_w4a16(const W4A16Args& a, cudaStream_t stream) {
-  const bool bf16 = a.dtype == KS_DTYPE_BF16;
+namespace {
+
+struct Geometry {
+  int mt, mtmax, n_tiles, k_steps, grid, max_parts;
+  size_t counter_bytes, slot_bytes;
+};
+
+Geometry geometry_of(const W4A16Args& a) {
+  Geometry g;
   const int mt_raw = static_cast<int>(a.m < 128 ? a.m : 128);
-  const int mt = (mt_raw + 15) & ~15;
-  const int mtmax = mt <= 32 ? 32 : 128;
-  const int n_tiles = static_cast<int>((a.n + kTileN - 1) / kTileN);
-  const int k_steps = static_cast<int>(a.k / kStepK);
-  const long long units = static_cast<long long>(n_tiles) * k_steps;
+  g.mt = (mt_raw + 15) & ~15;
+  g.mtmax = g.mt <= 32 ? 32 : 128;
+  g.n_tiles = static_cast<int>((a.n + kTileN - 1) / kTileN);
+  g.k_steps = static_cast<int>(a.k / kStepK);
+  const long long units = static_cast<long long>(g.n_tiles) * g.k_steps;
   const int sms = sm_count();
-  const int grid = static_cast<int>(units < sms ? units : sms);
-  const long long per_cta = units / grid;  // shortest run
-  const int max_parts = static_cast<int>((k_steps + per_cta - 1) / per_cta) + 1;
+  g.grid = static_cast<int>(units < sms ? units : sms);
+  const long long per_cta = units / g.grid;  // shortest run
+  g.max_parts = static_cast<int>((g.k_steps + per_cta - 1) / per_cta) + 1;
+  g.slot_bytes = static_cast<size_t>(g.n_tiles) * g.max_parts * g.mt * kTileN * sizeof(float);
+  g.counter_bytes = (static_cast<size_t>(g.n_tiles) * sizeof(unsigned int) + 255) & ~size_t(255);
+  return g;
+}
 
-  const size_t slot_bytes = static_cast<size_t>(n_tiles) * max_parts * mt * kTileN * sizeof(float);
-  const size_t counter_bytes = (static_cast<size_t>(n_tiles) * sizeof(unsigned int) + 255) & ~size_t(255);
-  uint8_t* scratch = static_cast<uint8_t*>(stream_scratch(stream, counter_bytes + slot_bytes));
-  if (scratch == nullptr) KSB_FAIL(KS_ERROR_OUT_OF_MEMORY, "ks_gemm_w4a16: workspace allocation failed");
-
+// Encodes the tensor maps and enqueues the kernel on scratch memory the caller
+// of this function has already obtained (counters first, then the slots).
+ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, uint8_t* scratch, unsigned int* fault_word,
+                          cudaStream_t stream) {
+  const bool bf16 = a.dtype == KS_DTYPE_BF16;
+  const int mt = g.mt, mtmax = g.mtmax, n_tiles = g.n_tiles, k_steps = g.k_steps, grid = g.grid,
+            max_parts = g.max_parts;
+  const size_t counter_bytes = g.counter_bytes;
   const CUtensorMapDataType dt16 = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap tm_w, tm_s, tm_z, tm_a;
   {
@@ -556,7 +571,7 @@ ks_status_t launch_w4a16(const W4A16Args& a, cudaStream_t stream) {
   p.bias = a.bias;
   p.counters = reinterpret_cast<unsigned int*>(scratch);
   p.slots = reinterpret_cast<float*>(scratch + counter_bytes);
-  p.fault_word = kernel_fault_word();
+  p.fault_word = fault_word;
   p.m = static_cast<int>(a.m);
   p.n = static_cast<int>(a.n);
   p.k = static_cast<int>(a.k);
@@ -576,6 +591,80 @@ ks_status_t launch_w4a16(const W4A16Args& a, cudaStream_t stream) {
   }
   return mtmax == 32 ? launch_t<__half, 32>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream)
                      : launch_t<__half, 128>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream);
+}
+
+}  // namespace
+
+ks_status_t launch_w4a16(const W4A16Args& a, cudaStream_t stream) {
+  const Geometry g = geometry_of(a);
+  uint8_t* scratch = static_cast<uint8_t*>(stream_scratch(stream, g.counter_bytes + g.slot_bytes));
+  if (scratch == nullptr) KSB_FAIL(KS_ERROR_OUT_OF_MEMORY, "ks_gemm_w4a16: workspace allocation failed");
+  return enqueue_w4a16(a, g, scratch, kernel_fault_word(), stream);
+}
+
+// ---------------------------------------------------------------------------
+// Variant for callers that must not allocate: the split-K slots and counters
+// live in a fixed array inside the library image instead of scratch memory
+// obtained from the CUDA allocator.
+//
+// `g_static_scratch` below is a __device__ array. In host code its name only
+// stands for the symbol: it is not an address a kernel may dereference. The
+// device address is asked for once per device (with that device current) with
+// cudaGetSymbolAddress, and that pointer is what the kernel receives.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;  // 16 MiB on every GPU that loads the library
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+std::mutex g_static_mutex;
+void* g_static_ptr[64] = {};
+
+// Device address of the array on the current device; resolved on the first
+// call per device. No allocation is involved.
+ks_status_t static_scratch_address(uint8_t** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e, "ks_gemm_w4a16_static_scratch");
+  if (dev < 0 || dev >= 64)
+    KSB_FAIL(KS_ERROR_INTERNAL, "ks_gemm_w4a16_static_scratch: device ordinal out of the supported range");
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return cuda_status(e, "ks_gemm_w4a16_static_scratch: cudaGetSymbolAddress");
+    if (ptr == nullptr)
+      KSB_FAIL(KS_ERROR_INTERNAL, "ks_gemm_w4a16_static_scratch: the scratch symbol resolved to a null address");
+    g_static_ptr[dev] = ptr;
+  }
+  *out = static_cast<uint8_t*>(g_static_ptr[dev]);
+  return KS_SUCCESS;
+}
+
+}  // namespace
+
+size_t w4a16_static_scratch_capacity() { return kStaticScratchBytes; }
+
+ks_status_t launch_w4a16_static(const W4A16Args& a, cudaStream_t stream) {
+  const Geometry g = geometry_of(a);
+  const size_t need = g.counter_bytes + g.slot_bytes;
+  if (need > kStaticScratchBytes) {
+    char msg[224];
+    snprintf(msg, sizeof(msg),
+             "ks_gemm_w4a16_static_scratch: this shape needs %zu bytes of split-K scratch, the built-in array "
+             "holds %zu; use ks_gemm_w4a16 or fewer rows per call",
+             need, kStaticScratchBytes);
+    KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE, msg);
+  }
+  uint8_t* scratch = nullptr;
+  ks_status_t st = static_scratch_address(&scratch);
+  if (st != KS_SUCCESS) return st;
+  // The array keeps whatever the previous call left. The kernel requires the
+  // per-tile arrival counters to be zero on entry (a clean run leaves them so,
+  // an aborted one may not); the slots are fully overwritten before being read.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, g.counter_bytes, stream);
+  if (e != cudaSuccess) return cuda_status(e, "ks_gemm_w4a16_static_scratch: cudaMemsetAsync");
+  return enqueue_w4a16(a, g, scratch, kernel_fault_word_if_ready(), stream);
 }
 
 }  // namespace sm100

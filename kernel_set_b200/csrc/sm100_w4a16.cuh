@@ -28,5 +28,11 @@ bool w4a16_eligible(const W4A16Args& a);
 // Encodes the tensor maps, sizes the scratch memory and enqueues one launch.
 ks_status_t launch_w4a16(const W4A16Args& a, cudaStream_t stream);
 
+// Same launch with the scratch taken from a fixed array in the library image;
+// performs no device or host allocation. Shapes whose scratch need exceeds
+// w4a16_static_scratch_capacity() are refused with KS_ERROR_UNSUPPORTED_SHAPE.
+ks_status_t launch_w4a16_static(const W4A16Args& a, cudaStream_t stream);
+size_t w4a16_static_scratch_capacity();
+
 }  // namespace sm100
 }  // namespace ksb

@@ -25,6 +25,22 @@ def gemm_w4a16(c: TensorLike, a: TensorLike, b_packed: TensorLike, scales: Tenso
     return c
 
 
+def gemm_w4a16_static_scratch(c: TensorLike, a: TensorLike, b_packed: TensorLike, scales: TensorLike,
+                              zeros: TensorLike, m: int, n: int, k: int, group_size: int, bias: TensorLike = None,
+                              dtype: Optional[int] = None, stream: TensorLike = None) -> TensorLike:
+    """:func:`gemm_w4a16` through the entry point that never allocates: the
+    kernel's split-K scratch is a fixed 16 MiB array inside the library. For
+    hosts that forbid allocator calls at run time; shapes needing more scratch
+    raise ``KernelSetError`` (UNSUPPORTED_SHAPE). All calls on a device share
+    the array: do not let two of them overlap on the GPU."""
+    dt = infer_dtype(a, dtype)
+    check(lib.ks_gemm_w4a16_static_scratch(ptr(c, name="c"), ptr(a, name="a"), ptr(b_packed, name="b_packed"),
+                                           ptr(scales, name="scales"), ptr(zeros, name="zeros"),
+                                           ptr(bias, name="bias"), int(m), int(n), int(k), int(group_size), dt,
+                                           default_stream(stream, a)), "ks_gemm_w4a16_static_scratch")
+    return c
+
+
 def gemm_fp8_blockwise(out: TensorLike, a_fp8: TensorLike, b_fp8: TensorLike, a_scale: TensorLike,
                        b_scale: TensorLike, m: int, n: int, k: int, block_n: int = 128, block_k: int = 128,
                        fp8_dtype: int = None, out_dtype: int = None, stream: TensorLike = None,
