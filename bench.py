@@ -46,6 +46,9 @@ def parse_args():
     p.add_argument("--impl", default="b200", choices=["b200", "reference"])
     p.add_argument("--no-extras", action="store_true", help="skip the W4A16 decode sweep and CPU baseline")
     p.add_argument("--m", type=int, default=M, help="rows of A (default: the headline 4096)")
+    p.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4", "cfg5"],
+                   help="cfg2: the headline GEMM (default); cfg4: MoE grouped FP8, expert-parallel; "
+                        "cfg5: row-parallel large GEMM with an all-reduce")
     return p.parse_args()
 
 
@@ -216,6 +219,163 @@ def w4a16_decode_sweep(ks, torch, dev, peaks):
     return res
 
 
+def block_quant_nk_device(w_nk):
+    """128 x 128 block quantization of a [N,K] fp32 weight on its own device: the
+    reference's input preparation (benchmarks/bench.py:1447-1461) written with
+    tensor ops. Returns (e4m3 [N,K], scales [N/128, K/128])."""
+    import torch
+    n, k = w_nk.shape
+    blocks = w_nk.view(n // 128, 128, k // 128, 128)
+    scale = (blocks.abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-12)
+    q = (blocks / scale[:, None, :, None]).to(torch.float8_e4m3fn).view(n, k)
+    return q, scale.contiguous()
+
+
+def timed(fn, steps, warmup, barrier, torch):
+    for _ in range(warmup):
+        fn()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_cfg5(args, torch, dist, ks, parallel, dev, rank, world):
+    """Row-parallel GEMM: A bf16 [16384, 28672], W e4m3 [8192, 28672], K split over the
+    ranks, bf16 partial outputs all-reduced. GEMM and all-reduce are timed separately."""
+    m5, n5, k5 = 16384, 8192, 28672
+    lo, hi = parallel.block_range(k5, rank, world)
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    a_sh = torch.randn(m5, hi - lo, generator=g, device=dev).to(torch.bfloat16)
+    w8, ws = block_quant_nk_device(torch.randn(n5, hi - lo, generator=g, device=dev) * 0.02)
+    a8 = torch.empty(m5, hi - lo, dtype=torch.float8_e4m3fn, device=dev)
+    a_s = torch.empty(m5, (hi - lo) // 128, dtype=torch.float32, device=dev)
+    out = torch.empty(m5, n5, dtype=torch.bfloat16, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def quant():
+        ks.quant.quantize_fp8_group(a8, a_s, a_sh, m5, hi - lo, 128)
+
+    def gemm():
+        ks.gemm.gemm_fp8_blockwise(out, a8, w8, a_s, ws, m5, n5, hi - lo, b_layout="nk")
+
+    def reduce():
+        if world > 1:
+            dist.all_reduce(out)
+
+    def step():
+        quant(); gemm(); reduce()
+
+    steps = max(3, min(args.steps, 20))
+    ms_step = timed(step, steps, max(args.warmup, 3), barrier, torch)
+    ms_quant = timed(quant, steps, 1, barrier, torch)
+    ms_gemm = timed(gemm, steps, 1, barrier, torch)
+    ms_red = timed(reduce, steps, 1, barrier, torch) if world > 1 else 0.0
+    t = torch.tensor([ms_step, ms_quant, ms_gemm, ms_red], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step, ms_quant, ms_gemm, ms_red = [float(v) for v in t.tolist()]
+    flops = 2.0 * m5 * n5 * k5
+    if rank == 0:
+        ring_bytes = 2.0 * (world - 1) / world * m5 * n5 * 2
+        print(json.dumps({
+            "metric": "fp8_blockwise_gemm_tflops", "value": flops / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3",
+            "data": "synthetic",
+            "config": {"workload": "row-parallel fp8_blockwise_gemm M=16384 N=8192 K=28672, K split, bf16 all-reduce",
+                       "k_per_gpu": hi - lo, "l2": "operands (0.7 GB per rank at 8 GPUs, 2 GB at 1) exceed L2"},
+            "gemm_us": ms_gemm * 1e3, "quantizer_us": ms_quant * 1e3, "allreduce_us": ms_red * 1e3,
+            "gemm_tflops_per_gpu": flops / world / (ms_gemm * 1e-3) / 1e12,
+            "allreduce_busbw_gbs": (ring_bytes / (ms_red * 1e-3) / 1e9) if world > 1 else None,
+            "gpu_launches": 2 * steps}), flush=True)
+
+
+def run_cfg4(args, torch, dist, ks, parallel, dev, rank, world):
+    """MoE layer, DeepSeek-V3 sizes: 4096 tokens, hidden 7168, 256 experts, intermediate 2048,
+    top-8. Experts are split contiguously over the ranks, tokens evenly; dispatch and combine
+    are all-to-alls. Weights are generated and block-quantized on the device, one expert at a time."""
+    tokens, hidden, experts, inter, topk = 4096, 7168, 256, 2048, 8
+    e_lo, e_hi = parallel.expert_range(experts, rank, world)
+    e_local = e_hi - e_lo
+    g = torch.Generator(device=dev).manual_seed(99 + rank)
+    w1 = torch.empty(e_local, 2 * inter, hidden, dtype=torch.float8_e4m3fn, device=dev)
+    s1 = torch.empty(e_local, 2 * inter // 128, hidden // 128, dtype=torch.float32, device=dev)
+    w2 = torch.empty(e_local, hidden, inter, dtype=torch.float8_e4m3fn, device=dev)
+    s2 = torch.empty(e_local, hidden // 128, inter // 128, dtype=torch.float32, device=dev)
+    for e in range(e_local):
+        w1[e], s1[e] = block_quant_nk_device(torch.randn(2 * inter, hidden, generator=g, device=dev) * 0.02)
+        w2[e], s2[e] = block_quant_nk_device(torch.randn(hidden, inter, generator=g, device=dev) * 0.02)
+    t_local = tokens // world
+    gt = torch.Generator().manual_seed(7)  # routing is global and identical on every rank
+    logits = torch.randn(tokens, experts, generator=gt)
+    probs = torch.softmax(logits.float(), dim=-1)
+    wts, ids = torch.topk(probs, topk, dim=-1)
+    wts = wts / wts.sum(-1, keepdim=True)
+    x = torch.randn(tokens, hidden, generator=gt).to(torch.bfloat16)
+    sl = slice(rank * t_local, (rank + 1) * t_local)
+    x_l, ids_l, w_l = x[sl].to(dev), ids[sl], wts[sl].to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        return parallel.expert_parallel_moe(x_l, ids_l, w_l, w1, s1, w2, s2, experts)
+
+    steps = max(3, min(args.steps, 10))
+    ms_step = timed(step, steps, 3, barrier, torch)
+    # the two grouped GEMMs alone, on this rank's routed rows
+    order, per_expert, send_counts = parallel.plan_dispatch(ids, experts, 1)
+    counts_local = per_expert[e_lo:e_hi]
+    offs = torch.zeros(e_local + 1, dtype=torch.int32)
+    offs[1:] = torch.cumsum(counts_local, 0).to(torch.int32)
+    rows = int(offs[-1])
+    offs_d = offs.to(dev)
+    xa = torch.randn(rows, hidden, generator=g, device=dev).to(torch.bfloat16)
+    xa8, xas = ks.dispatch.per_token_group_quant(xa)
+    ha = torch.randn(rows, inter, generator=g, device=dev).to(torch.bfloat16)
+    ha8, has = ks.dispatch.per_token_group_quant(ha)
+
+    def gemms():
+        ks.dispatch.moe(xa8, w1, offs_d, n=2 * inter, k=hidden, a_scale=xas, b_scale=s1, b_layout="nk")
+        ks.dispatch.moe(ha8, w2, offs_d, n=hidden, k=inter, a_scale=has, b_scale=s2, b_layout="nk")
+
+    ms_gemm = timed(gemms, steps, 2, barrier, torch)
+    t = torch.tensor([ms_step, ms_gemm, float(rows)], dtype=torch.float64, device=dev)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms_step, ms_gemm, rows_all = float(tmax[0]), float(tmax[1]), float(t[2])
+    else:
+        ms_step, ms_gemm, rows_all = float(t[0]), float(t[1]), float(t[2])
+    flops = 2.0 * rows_all * (2 * inter * hidden + hidden * inter)
+    weight_bytes = e_local * (2 * inter * hidden + hidden * inter)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "moe_grouped_fp8_gemm_tflops", "value": flops / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+            "config": {"workload": "MoE grouped FP8 block-scaled: 4096 tokens, hidden 7168, 256 experts, inter 2048, "
+                                   "top-8; experts split over ranks, all-to-all dispatch and combine",
+                       "experts_per_gpu": e_local, "routed_rows": rows_all,
+                       "l2": f"{weight_bytes / 1e9:.2f} GB of expert weights per rank, far larger than L2"},
+            "grouped_gemms_us": ms_gemm * 1e3,
+            "grouped_gemms_tflops_per_gpu": flops / world / (ms_gemm * 1e-3) / 1e12,
+            "grouped_gemms_weight_gbs": weight_bytes / (ms_gemm * 1e-3) / 1e9,
+            "gpu_launches": 4 * steps}), flush=True)
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -237,6 +397,12 @@ def main():
 
     import kernel_set_b200 as ks
     from kernel_set_b200 import parallel
+
+    if args.workload != "cfg2":
+        (run_cfg5 if args.workload == "cfg5" else run_cfg4)(args, torch, dist, ks, parallel, dev, rank, world)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     peaks = measured_peaks()
     m = args.m

@@ -128,3 +128,110 @@ def received_to_expert_major(recv_counts_matrix: torch.Tensor):
     offsets = torch.zeros(per + 1, dtype=torch.int32)
     offsets[1:] = torch.cumsum(counts.sum(0), 0).to(torch.int32)
     return perm, offsets
+
+
+# ------------------------------------------------------------------------------
+# Sharded operators. `ops` supplies the single-device kernels:
+#   ops.quant(x, group_size) -> (codes, scales)
+#   ops.fp8_gemm(a8, b8, a_scale, b_scale, b_layout, out_dtype) -> out
+#   ops.grouped_fp8_gemm(a8, b8, expert_offsets, a_scale, b_scale, n, k, b_layout) -> out
+# The default is this library (CUDA tensors). Anything with the same three
+# methods can stand in, which is how the CPU tests drive the sharding logic.
+# ------------------------------------------------------------------------------
+class LibraryOps:
+    """The CUDA library as the per-device backend of the sharded operators."""
+
+    def quant(self, x, group_size=BLOCK):
+        from . import dispatch
+        return dispatch.per_token_group_quant(x, group_size=group_size)
+
+    def fp8_gemm(self, a8, b8, a_scale, b_scale, b_layout="nk", out_dtype=torch.bfloat16):
+        from . import dispatch
+        return dispatch.fp8_gemm_blockwise(a8, b8, a_scale, b_scale, b_layout=b_layout, out_dtype=out_dtype)
+
+    def grouped_fp8_gemm(self, a8, b8, expert_offsets, a_scale, b_scale, n, k, b_layout="nk"):
+        from . import dispatch
+        return dispatch.moe(a8, b8, expert_offsets, n=n, k=k, a_scale=a_scale, b_scale=b_scale, b_layout=b_layout)
+
+
+def column_parallel_linear(x: torch.Tensor, w8_shard: torch.Tensor, ws_shard: torch.Tensor, ops=None,
+                           b_layout: str = "nk") -> torch.Tensor:
+    """x [M,K] (replicated) times this rank's column shard of the weight: quantize
+    locally, multiply, keep the output sharded [M, N/g]. No collective."""
+    ops = ops or LibraryOps()
+    a8, a_s = ops.quant(x, BLOCK)
+    return ops.fp8_gemm(a8, w8_shard, a_s, ws_shard, b_layout, torch.bfloat16)
+
+
+def row_parallel_linear(x_shard: torch.Tensor, w8_kshard: torch.Tensor, ws_kshard: torch.Tensor, ops=None,
+                        b_layout: str = "nk", group=None, reduce_dtype=torch.bfloat16) -> torch.Tensor:
+    """x_shard [M, K/g] (this rank's K-slice of the activation) times this rank's
+    K-slice of the weight, then one all-reduce of the partial outputs. The 1 x 128
+    activation groups never straddle ranks because K-slices are whole blocks."""
+    ops = ops or LibraryOps()
+    a8, a_s = ops.quant(x_shard, BLOCK)
+    partial = ops.fp8_gemm(a8, w8_kshard, a_s, ws_kshard, b_layout, reduce_dtype)
+    return all_reduce_partials(partial, group)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for a [rows, 2*I] tensor holding gate then up."""
+    i = gate_up.shape[1] // 2
+    g = gate_up[:, :i].float()
+    return (torch.nn.functional.silu(g) * gate_up[:, i:].float()).to(gate_up.dtype)
+
+
+def expert_parallel_moe(tokens: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                        w1_8: torch.Tensor, w1_s: torch.Tensor, w2_8: torch.Tensor, w2_s: torch.Tensor,
+                        num_experts: int, ops=None, group=None) -> torch.Tensor:
+    """One MoE layer with experts split contiguously over the ranks.
+
+    tokens [T_local, H] bf16 (this rank's tokens); topk_ids / topk_weights
+    [T_local, k]; w1_8 [E_local, 2I, H] with w1_s [E_local, 2I/128, H/128];
+    w2_8 [E_local, H, I] with w2_s [E_local, H/128, I/128] (this rank's experts,
+    weights stored [N,K]). Steps: sort the (token, slot) pairs by expert ->
+    exchange counts -> all-to-all the rows to their expert's rank -> regroup by
+    local expert -> grouped FP8 GEMM (gate/up) -> SwiGLU -> quantize -> grouped
+    FP8 GEMM (down) -> all-to-all back -> weighted sum per token.
+    Returns [T_local, H] bf16."""
+    ops = ops or LibraryOps()
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    t_local, hidden = tokens.shape
+    k = topk_ids.shape[1]
+    dev = tokens.device
+    order, per_expert, send_counts = plan_dispatch(topk_ids.cpu(), num_experts, world)
+    rows = tokens.repeat_interleave(k, dim=0)[order.to(dev)]          # (token, slot) pairs sorted by expert
+    if world > 1:
+        recv_matrix = exchange_counts(per_expert.to(dev), num_experts, world, group).cpu()
+        recv_counts = recv_matrix.sum(1)
+        received = all_to_all_rows(rows, send_counts.tolist(), recv_counts.tolist(), group)
+    else:
+        per = -(-num_experts // world)
+        recv_matrix = per_expert.view(1, per)
+        recv_counts = recv_matrix.sum(1)
+        received = rows
+    perm, offsets = received_to_expert_major(recv_matrix)
+    x = received[perm.to(dev)]
+    offs_dev = offsets.to(dev)
+    e_local = w1_8.shape[0]
+    inter2, inter = w1_8.shape[1], w2_8.shape[2]
+    if x.shape[0] > 0:
+        x8, x_s = ops.quant(x, BLOCK)
+        h = ops.grouped_fp8_gemm(x8, w1_8, offs_dev, x_s, w1_s, inter2, hidden, "nk")
+        act = swiglu(h)
+        a8, a_s = ops.quant(act, BLOCK)
+        y = ops.grouped_fp8_gemm(a8, w2_8, offs_dev, a_s, w2_s, hidden, inter, "nk")
+    else:
+        y = x.new_zeros((0, hidden))
+    assert e_local * 1 >= 0
+    # undo the regrouping, send every row back to the rank its token lives on
+    back = torch.empty_like(y)
+    back[perm.to(dev)] = y
+    if world > 1:
+        returned = all_to_all_rows(back, recv_counts.tolist(), send_counts.tolist(), group)
+    else:
+        returned = back
+    unsorted = torch.empty_like(returned)
+    unsorted[order.to(dev)] = returned
+    out = (unsorted.view(t_local, k, hidden).float() * topk_weights.to(dev).float().unsqueeze(-1)).sum(1)
+    return out.to(tokens.dtype)
