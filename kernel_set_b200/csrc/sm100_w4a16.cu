@@ -14,7 +14,10 @@
 //                 = 8 KB straight from HBM plus the group's 128 scales and
 //                 zero-points (2 x 256 B), ten stages deep
 //   warp 2        activation producer (TMA): the K-slice [tokens x 128] (from L2)
-//   warps 4-11    dequantisation: 8 packed bytes -> 16 weights per step:
+//   warps 4-11    dequantisation, two groups of four warps working on alternate
+//                 units (a thread then owns 128 weights of a unit, which
+//                 amortises the per-unit waits, fences and scale preparation):
+//                 8 packed bytes -> 16 weights per step:
 //                 nibble -> (128 + q) by byte-permute into a bf16 pattern,
 //                 minus (128 + zero), times scale, two packed 16-bit ops;
 //                 written as the MN-major, 128-byte-swizzled UMMA A operand
@@ -50,7 +53,8 @@ constexpr int kRawBytes = (kStepK / 2) * kTileN;      // 8192
 constexpr int kRawStage = kRawBytes + 2 * 256;        // + scales + zeros of the step
 constexpr int kDeqBytes = kStepK * kTileN * 2;        // 32768: dequantised UMMA operand
 constexpr int kThreads = 512;
-constexpr int kDeqWarps = 8;
+constexpr int kDeqWarps = 8;       // two groups of four; a group takes every other unit
+constexpr int kDeqGroupWarps = 4;
 
 template <int MTMAX>
 struct Cfg {
@@ -101,7 +105,7 @@ template <> struct Pack16<__nv_bfloat16> {
   using V2 = __nv_bfloat162;
   static constexpr uint32_t kMagicBytes = 0x43434343u;  // high byte of bf16(128 + q)
   static constexpr float kMagic = 128.0f;
-  static constexpr float kMaxZero = 127.0f;
+  static constexpr uint32_t kMaxZeroBits = 0x42FEu;     // bf16(127)
   __device__ static V2 from_bits(uint32_t b) { return *reinterpret_cast<V2*>(&b); }
   __device__ static uint32_t bits(V2 v) { return *reinterpret_cast<uint32_t*>(&v); }
   __device__ static V2 splat(float f) { return __float2bfloat162_rn(f); }
@@ -113,7 +117,7 @@ template <> struct Pack16<__half> {
   using V2 = __half2;
   static constexpr uint32_t kMagicBytes = 0x64646464u;  // high byte of f16(1024 + q)
   static constexpr float kMagic = 1024.0f;
-  static constexpr float kMaxZero = 1023.0f;
+  static constexpr uint32_t kMaxZeroBits = 0x63FEu;     // f16(1023)
   __device__ static V2 from_bits(uint32_t b) { return *reinterpret_cast<V2*>(&b); }
   __device__ static uint32_t bits(V2 v) { return *reinterpret_cast<uint32_t*>(&v); }
   __device__ static V2 splat(float f) { return __float2half2_rn(f); }
@@ -165,14 +169,14 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kRawStages; ++s) {
       mbar_init(bar_raw_full + 8 * s, 1);
-      mbar_init(bar_raw_empty + 8 * s, kDeqWarps);
+      mbar_init(bar_raw_empty + 8 * s, kDeqGroupWarps);
     }
     for (int s = 0; s < C::kActStages; ++s) {
       mbar_init(bar_act_full + 8 * s, 1);
       mbar_init(bar_act_empty + 8 * s, 1);
     }
     for (int s = 0; s < C::kDeqStages; ++s) {
-      mbar_init(bar_deq_full + 8 * s, kDeqWarps);
+      mbar_init(bar_deq_full + 8 * s, kDeqGroupWarps);
       mbar_init(bar_deq_empty + 8 * s, 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -287,45 +291,52 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
   } else if (warp >= 4 && warp < 4 + kDeqWarps) {
     // ----------------------------- dequantisation -----------------------------
-    const int tt = threadIdx.x - 128;
+    const int group = (warp - 4) >> 2;          // 0: even units of this CTA's run, 1: odd units
+    const int tt = (threadIdx.x - 128) & 127;   // thread inside its group
     const int oct = tt & 15;   // 8 weight columns: n_local = 8*oct .. 8*oct+7
-    const int rg = tt >> 4;    // 4 packed byte-rows: k_local = 8*rg .. 8*rg+7
+    const int rg = tt >> 4;    // 8 packed byte-rows: k_local = 16*rg .. 16*rg+15
     const uint32_t atom_off = (oct >> 3) * 16384u;
     const uint32_t chunk = oct & 7;
-    uint32_t it = 0;
+    const V2 magic2 = P16::splat(P16::kMagic);
     {
-      for (long long u = u_begin; u < u_end; ++u, ++it) {
+      for (long long u = u_begin + group; u < u_end; u += 2) {
+        const uint32_t it = static_cast<uint32_t>(u - u_begin);
         const uint32_t sr = it % C::kRawStages, pr = (it / C::kRawStages) & 1u;
         const uint32_t sd = it % C::kDeqStages, pd = (it / C::kDeqStages) & 1u;
         if (!mbar_wait(wctx, bar_raw_full + 8 * sr, pr, 0x400u + sr)) break;
         const uint8_t* raw = rawst_ptr + sr * kRawStage;
-        // group constants of this thread's 8 columns
+        // the packed bytes this thread owns, and the group constants of its 8 columns
+        uint2 pk[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pk[i] = *reinterpret_cast<const uint2*>(raw + (rg * 8 + i) * kTileN + oct * 8);
         const uint4 s4 = *reinterpret_cast<const uint4*>(raw + kRawBytes + oct * 16);
         uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
         if (p.has_zeros) z4 = *reinterpret_cast<const uint4*>(raw + kRawBytes + 256 + oct * 16);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_raw_empty + 8 * sr);  // the packed stage is in registers
         const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
         const uint32_t zw[4] = {z4.x, z4.y, z4.z, z4.w};
         V2 sc[4], zz[4];
-        bool simple = true;
+        // (magic + zero) must be exact and |q - zero| small enough to be exact too:
+        // true for non-negative integer zero-points up to kMaxZero, which a packed
+        // add / subtract round trip plus two range checks establish.
+        uint32_t bad = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           sc[j] = P16::from_bits(sw[j]);
           const V2 z = P16::from_bits(zw[j]);
-          const float z0 = P16::lo(z), z1 = P16::hi(z);
-          simple = simple && (z0 == rintf(z0)) && (z1 == rintf(z1)) && z0 >= 0.f && z1 >= 0.f &&
-                   z0 <= P16::kMaxZero && z1 <= P16::kMaxZero;
-          zz[j] = P16::make(z0 + P16::kMagic, z1 + P16::kMagic);  // exact for integer zero-points
+          zz[j] = __hadd2(z, magic2);
+          const uint32_t back = P16::bits(__hsub2(zz[j], magic2));
+          bad |= (back ^ zw[j]) | (zw[j] & 0x80008000u);
+          bad |= ((zw[j] & 0xFFFFu) > P16::kMaxZeroBits) ? 1u : 0u;
+          bad |= ((zw[j] >> 16) > P16::kMaxZeroBits) ? 1u : 0u;
         }
-        uint2 pk[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) pk[i] = *reinterpret_cast<const uint2*>(raw + (rg * 4 + i) * kTileN + oct * 8);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_raw_empty + 8 * sr);  // the packed stage is in registers
+        const bool simple = bad == 0u;
         if (!mbar_wait(wctx, bar_deq_empty + 8 * sd, pd ^ 1u, 0x480u + sd)) break;
         uint8_t* deq = deq_ptr + sd * kDeqBytes + atom_off;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r_even = rg * 8 + 2 * i;
+        for (int i = 0; i < 8; ++i) {
+          const int r_even = rg * 16 + 2 * i;
           uint32_t even[4], odd[4];
           if (simple) {
             const uint32_t words[2] = {pk[i].x, pk[i].y};
@@ -446,13 +457,24 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             __threadfence();
             const float* tile_slots = p.slots + static_cast<size_t>(tile) * p.max_parts * (static_cast<size_t>(p.mt) * kTileN);
             const float bv = (bias != nullptr && n_ok) ? to_f32<T>(bias[n]) : 0.f;
-            for (int mm = 0; mm < p.mt; ++mm) {
-              const int m = m0 + mm;
-              if (m >= p.m) break;
-              float sum = 0.f;
-              for (int q = 0; q < parts; ++q)
-                sum += __ldcg(tile_slots + (static_cast<size_t>(q) * p.mt + mm) * kTileN + n_local);
-              if (n_ok) c[static_cast<size_t>(m) * p.n + n] = from_f32<T>(sum + bv);
+            // eight rows at a time, all their loads issued before any is consumed
+            for (int mm0 = 0; mm0 < p.mt && m0 + mm0 < p.m; mm0 += 8) {
+              float sum[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) sum[j] = 0.f;
+              for (int q = 0; q < parts; ++q) {
+                const float* src = tile_slots + (static_cast<size_t>(q) * p.mt + mm0) * kTileN + n_local;
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + j * kTileN);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sum[j] += v[j];
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int m = m0 + mm0 + j;
+                if (m < p.m && n_ok) c[static_cast<size_t>(m) * p.n + n] = from_f32<T>(sum[j] + bv);
+              }
             }
           }
           named_barrier_sync(1, 128);  // last_flag may be rewritten only after everyone has read it
