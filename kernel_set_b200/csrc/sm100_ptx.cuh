@@ -73,6 +73,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Same test, but the thread may stay suspended in hardware for up to `hint_ns`
+// while the phase is incomplete (it is still resumed when the phase completes).
+// For waits known to be long: a sleeping waiter leaves the issue slots of its
+// scheduler to the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Shared state of a CTA's bounded waits.
 struct WaitCtx {
   volatile uint32_t* abort_flag;  // shared memory, zero while healthy
@@ -82,6 +100,29 @@ struct WaitCtx {
 // Waits for the phase with the given parity to complete. Returns false when
 // another waiter of this CTA has already given up or when this one times out;
 // `code` identifies the wait site in the recorded fault word.
+__device__ __forceinline__ bool mbar_wait(const WaitCtx& ctx, uint32_t bar, uint32_t parity, uint32_t code);
+
+// Bounded wait for barriers that normally take thousands of cycles to complete
+// (an accumulator that needs a whole run of K-steps): polls with a suspend hint.
+__device__ __forceinline__ bool mbar_wait_long(const WaitCtx& ctx, uint32_t bar, uint32_t parity, uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+    if (*ctx.abort_flag != 0u) return false;
+    if (global_ns() - t0 > kWaitLimitNs) {
+      *ctx.abort_flag = 1u;
+      if (ctx.fault_word != nullptr) {
+        *reinterpret_cast<volatile unsigned int*>(ctx.fault_word) = 0x80000000u | code;
+        __threadfence_system();
+      }
+      return false;
+    }
+  }
+}
+
 __device__ __forceinline__ bool mbar_wait(const WaitCtx& ctx, uint32_t bar, uint32_t parity, uint32_t code) {
   // Fast path: plain polling, no timer and no shared-memory traffic besides the
   // barrier itself. Each failed try_wait may itself block for a short,

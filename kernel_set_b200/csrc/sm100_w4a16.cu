@@ -16,15 +16,15 @@
 //   warp 2        activation producer (TMA): the K-slice [tokens x 128] (from L2)
 //   warps 4-11    dequantisation, two groups of four warps working on alternate
 //                 units (a thread then owns 128 weights of a unit, which
-//                 amortises the per-unit waits, fences and scale preparation):
+//                 amortises the per-unit waits, fences and scale preparation;
+//                 two groups of eight warps measured slower):
 //                 8 packed bytes -> 16 weights per step:
 //                 nibble -> (128 + q) by byte-permute into a bf16 pattern,
 //                 minus (128 + zero), times scale, two packed 16-bit ops;
 //                 written as the MN-major, 128-byte-swizzled UMMA A operand
-//   warp 1        MMA issuer: 8 x tcgen05.mma kind::f16 (M128, N=tokens, K16)
-//                 per step into a TMEM accumulator
+//   warps 1, 3    MMA issuers: 4 x tcgen05.mma kind::f16 (M128, N=tokens, K16)
+//                 each per step, into disjoint TMEM accumulators
 //   warps 12-15   epilogue: TMEM -> registers -> C, or -> an fp32 partial slot
-//   warp 3        idle
 // Work is cut stream-K style: the (column tile, K-step) units are dealt to the
 // CTAs in equal contiguous runs, so every SM streams the same number of bytes
 // whatever N is. A column tile whose K range is shared by several CTAs is
@@ -173,14 +173,14 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
     for (int s = 0; s < C::kActStages; ++s) {
       mbar_init(bar_act_full + 8 * s, 1);
-      mbar_init(bar_act_empty + 8 * s, 1);
+      mbar_init(bar_act_empty + 8 * s, 2);   // both MMA issuers commit
     }
     for (int s = 0; s < C::kDeqStages; ++s) {
       mbar_init(bar_deq_full + 8 * s, kDeqGroupWarps);
-      mbar_init(bar_deq_empty + 8 * s, 1);
+      mbar_init(bar_deq_empty + 8 * s, 2);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_full + 8 * b, 2);
       mbar_init(bar_acc_empty + 8 * b, 4);
     }
     *abort_flag = 0u;
@@ -252,8 +252,13 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         tma_load_2d_elect(dst + p.mt * 128, &tm_a, full, step * kStepK + 64, mtile * p.mt);
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------ MMA issuers ------------------------------
+    // Issuing one tcgen05.mma costs its thread ~55 cycles; eight per unit from one
+    // thread would set the pace of the whole kernel. Two warps issue four each,
+    // into disjoint accumulators (an accumulator must have a single issuer).
+    const int mma_half = warp == 3 ? 1 : 0;
+    constexpr int kHalfAccs = C::kAccs / 2;
     uint32_t it = 0, seg = 0;
     {
       int step = static_cast<int>(u_begin % p.k_steps);
@@ -273,14 +278,15 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           const uint32_t a_src = act_base + sa * C::kActStage;
           const uint32_t d_tmem = tmem_base + buf * (C::kAccs * MTMAX);
 #pragma unroll
-          for (int kk = 0; kk < kStepK / 16; ++kk) {
+          for (int kq = 0; kq < kStepK / 32; ++kq) {
+            const int kk = mma_half * (kStepK / 32) + kq;
             // Weights: MN-major, 64-column atoms 16 KB apart, 8-k groups 1024 B
             // apart, 16 k = 2048 B per instruction. Tokens: K-major, two 64-k
             // atoms of mt rows, 32 B per instruction inside an atom.
             const uint64_t w_desc = umma_smem_desc_sw128(w_src + kk * 2048, 16384, 1024);
             const uint64_t a_desc = umma_smem_desc_sw128(a_src + (kk >> 2) * (p.mt * 128) + (kk & 3) * 32, 16, 1024);
-            umma_f16_elect(d_tmem + (kk % C::kAccs) * MTMAX, w_desc, a_desc, p.idesc,
-                           (seg_first && kk < C::kAccs) ? 0u : 1u);
+            umma_f16_elect(d_tmem + (mma_half * kHalfAccs + (kq % kHalfAccs)) * MTMAX, w_desc, a_desc, p.idesc,
+                           (seg_first && kq < kHalfAccs) ? 0u : 1u);
           }
           tc_commit_elect(bar_deq_empty + 8 * sd);
           tc_commit_elect(bar_act_empty + 8 * sa);
@@ -382,11 +388,11 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         if (lane == 0) mbar_arrive(bar_deq_full + 8 * sd);
       }
     }
-  } else if (warp >= 12) {
+  } else if (warp >= 4 + kDeqWarps) {
     // -------------------------------- epilogue --------------------------------
     const int quarter = warp & 3;
     const int n_local = quarter * 32 + lane;   // TMEM lane = weight column inside the tile
-    const int et = threadIdx.x - 384;
+    const int et = threadIdx.x - (128 + kDeqWarps * 32);
     T* c = static_cast<T*>(p.c);
     const T* bias = static_cast<const T*>(p.bias);
     uint32_t seg = 0;
@@ -404,7 +410,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const uint32_t buf = seg & 1u, pacc = (seg >> 1) & 1u;
         ++seg;
         u = seg_end;
-        if (!mbar_wait(wctx, bar_acc_full + 8 * buf, pacc, 0x500u + buf)) break;
+        if (!mbar_wait_long(wctx, bar_acc_full + 8 * buf, pacc, 0x500u + buf)) break;
         tc_fence_after_sync();
         const int n = tile * kTileN + n_local;
         const bool n_ok = n < p.n;
