@@ -64,7 +64,10 @@ ks_status_t run(sm100::Fp8GemmArgs& a, ks_stream_t stream) {
   cudaStream_t s = as_stream(stream);
   const int path = env_path();
   a.force_bn = env_bn();
-  if (path != 1 && sm100::fp8_blockwise_eligible(a)) return sm100::launch_fp8_blockwise(a, s);
+  if (path != 1 && sm100::fp8_blockwise_eligible(a)) {
+    if (a.force_bn == 0 && sm100::fp8_blockwise_pair_eligible(a)) return sm100::launch_fp8_blockwise_pair(a, s);
+    return sm100::launch_fp8_blockwise(a, s);
+  }
   if (path == 2)
     KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE, std::string(a.where) + ": shape not eligible for the tcgen05 kernel");
   const int64_t tiles_m = (a.m + general::kTM - 1) / general::kTM + a.num_experts;

@@ -30,6 +30,7 @@
 
 #include "common.cuh"
 #include "sm100_fp8_gemm.cuh"
+#include "sm100_fp8_store.cuh"
 #include "sm100_host.cuh"
 #include "sm100_ptx.cuh"
 
@@ -119,58 +120,6 @@ __device__ __forceinline__ bool locate_tile(const Params& p, const int* prefix, 
     tc->row_end = offs[lo + 1];
     tc->n0 = (t - mt * p.tiles_n) * BN;
     return true;
-  }
-}
-
-template <typename OutT>
-__device__ __forceinline__ void store_16(OutT* dst, const float* v, bool vec, int valid_cols);
-
-// Stores 16 consecutive outputs of one row; `valid_cols` of them exist.
-template <>
-__device__ __forceinline__ void store_16<float>(float* dst, const float* v, bool vec, int valid_cols) {
-  if (vec && valid_cols >= 16) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-      if (i < valid_cols) dst[i] = v[i];
-  }
-}
-template <>
-__device__ __forceinline__ void store_16<__nv_bfloat16>(__nv_bfloat16* dst, const float* v, bool vec,
-                                                        int valid_cols) {
-  if (vec && valid_cols >= 16) {
-    uint32_t w[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-      w[i] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-    reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-      if (i < valid_cols) dst[i] = __float2bfloat16_rn(v[i]);
-  }
-}
-template <>
-__device__ __forceinline__ void store_16<__half>(__half* dst, const float* v, bool vec, int valid_cols) {
-  if (vec && valid_cols >= 16) {
-    uint32_t w[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-      w[i] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-    reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-      if (i < valid_cols) dst[i] = __float2half_rn(v[i]);
   }
 }
 

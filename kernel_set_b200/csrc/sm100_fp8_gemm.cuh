@@ -33,5 +33,10 @@ bool fp8_blockwise_eligible(const Fp8GemmArgs& a);
 // Encodes the tensor maps and enqueues one persistent launch on `stream`.
 ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream);
 
+// CTA-pair (cta_group::2) kernel for dense problems: 256 x 256 tiles per pair of
+// SMs. `eligible` also consults KS_B200_FP8_PAIR (0 = never, 1 = whenever legal).
+bool fp8_blockwise_pair_eligible(const Fp8GemmArgs& a);
+ks_status_t launch_fp8_blockwise_pair(const Fp8GemmArgs& a, cudaStream_t stream);
+
 }  // namespace sm100
 }  // namespace ksb

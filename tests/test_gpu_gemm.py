@@ -100,6 +100,33 @@ def test_fp8_tcgen05_kernel(ks, cuda, m, n, k, layout, bn_tile, out_dtype, fp8):
         assert orc.rel_frobenius(out, gen_out) < 1e-5
 
 
+@pytest.mark.parametrize("m,n,k,layout,out_dtype,fp8", [
+    (256, 256, 128, "nk", torch.float32, "e4m3"),      # one pair tile, one K-block
+    (256, 256, 128, "kn", torch.float32, "e4m3"),
+    (512, 512, 1024, "nk", torch.bfloat16, "e4m3"),
+    (512, 512, 1024, "kn", torch.bfloat16, "e4m3"),
+    (300, 336, 400, "nk", torch.float16, "e4m3"),      # ragged M, N, K
+    (300, 336, 400, "kn", torch.bfloat16, "e5m2"),
+    (130, 7168, 512, "nk", torch.bfloat16, "e4m3"),    # second CTA of each pair nearly empty
+    (2048, 2048, 7168, "nk", torch.bfloat16, "e4m3"),  # several tiles per pair, 56 K-blocks
+    (2048, 2048, 7168, "kn", torch.bfloat16, "e4m3"),
+])
+def test_fp8_cta_pair_kernel(ks, cuda, m, n, k, layout, out_dtype, fp8):
+    a8, a_s, b8, b_s = fp8_inputs(m, n, k, seed=m * 3 + n + k, fp8=fp8)
+    ref32, noise = fp8_reference(a8, a_s, b8, b_s)
+    old = os.environ.get("KS_B200_FP8_PAIR")
+    os.environ["KS_B200_FP8_PAIR"] = "1"
+    try:
+        with fp8_path("tcgen05"):
+            out = run_fp8(ks, cuda, a8, a_s, b8, b_s, layout, out_dtype)
+    finally:
+        if old is None:
+            os.environ.pop("KS_B200_FP8_PAIR", None)
+        else:
+            os.environ["KS_B200_FP8_PAIR"] = old
+    check_gemm(out, ref32, noise, f"cta pair {m}x{n}x{k} {layout}")
+
+
 def test_fp8_golden(ks, cuda):
     for tag in ("a", "b"):
         g = golden(f"fp8_blockwise_{tag}.npz")
