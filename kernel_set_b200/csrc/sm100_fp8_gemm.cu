@@ -27,6 +27,7 @@
 // Roofline: tensor-bound for M >= ~1024 (2*M*N*K flop over 4.5 PFLOP/s dense
 // FP8); bytes per launch M*K + N*K + M*N*sizeof(out) + scales.
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "sm100_fp8_gemm.cuh"
@@ -71,8 +72,14 @@ struct Cfg {
   static constexpr int kRegsIssue = kEpiCols == 64 ? 32 : 40;
   static constexpr int kRegsEpi = kEpiCols == 64 ? 112 : 232;
   static constexpr int kTmemCols = 2 * BN;
-  // ring + 1024 B alignment slack + barriers/flags + grouped tile prefix and offsets
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + 2 * 4 * (kMaxExperts + 1);
+  // Dense problems stage the finished tile for TMA stores: 32 rows x 128 B per epilogue warp.
+  static constexpr int kStoreStageBytes = 32 * 128;
+  // ring + 1024 B alignment slack + barriers/flags, then either the store staging
+  // (dense) or the tile prefix and offsets (grouped)
+  static constexpr int smem_bytes(bool grouped) {
+    return kStages * kStageBytes + 1024 + 256 +
+           (grouped ? 2 * 4 * (kMaxExperts + 1) : kEpiWarps * kStoreStageBytes);
+  }
 };
 
 struct Params {
@@ -89,6 +96,7 @@ struct Params {
   int tiles_m;  // dense only
   uint32_t idesc;
   int vec_store;  // 16-byte output stores are legal
+  int tma_store;  // dense problems: finished tiles leave through shared memory and TMA stores
 };
 
 struct TileCoord {
@@ -123,6 +131,9 @@ __device__ __forceinline__ bool locate_tile(const Params& p, const int* prefix, 
   }
 }
 
+static_assert(Cfg<256>::smem_bytes(false) <= 232448 && Cfg<256>::smem_bytes(true) <= 232448 &&
+                  Cfg<128>::smem_bytes(false) <= 232448 && Cfg<128>::smem_bytes(true) <= 232448,
+              "shared memory layout exceeds the 227 KB a CTA can opt in to");
 static_assert(128 * Cfg<256>::kRegsIssue + (Cfg<256>::kThreads - 128) * Cfg<256>::kRegsEpi <=
                   Cfg<256>::kThreads * ((65536 / Cfg<256>::kThreads) & ~7),
               "setmaxnreg budgets exceed the register pool the CTA is launched with");
@@ -130,13 +141,16 @@ static_assert(128 * Cfg<256>::kRegsIssue + (Cfg<256>::kThreads - 128) * Cfg<256>
 template <int BN, bool NT, bool GROUPED, typename OutT>
 __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
 fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                          const Params p) {
+                          const __grid_constant__ CUtensorMap tm_c, const Params p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t ring = (raw_addr + 1023u) & ~1023u;  // 1024-byte aligned for the 128 B swizzle
-  uint8_t* ctrl = smem_raw + (ring - raw_addr) + C::kStages * C::kStageBytes;
-  const uint32_t ctrl_addr = ring + C::kStages * C::kStageBytes;
+  // dense: [ring | store staging | control]; grouped: [ring | control | prefix, offsets]
+  constexpr int kStagingBytes = GROUPED ? 0 : C::kEpiWarps * C::kStoreStageBytes;
+  const uint32_t staging = ring + C::kStages * C::kStageBytes;
+  uint8_t* ctrl = smem_raw + (ring - raw_addr) + C::kStages * C::kStageBytes + kStagingBytes;
+  const uint32_t ctrl_addr = staging + kStagingBytes;
   // control block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem slot | abort flag
   const uint32_t bar_full = ctrl_addr;
   const uint32_t bar_empty = ctrl_addr + 8 * C::kStages;
@@ -164,6 +178,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     fence_barrier_init();
     prefetch_tensormap(&tm_a);
     prefetch_tensormap(&tm_b);
+    if (!GROUPED && p.tma_store) prefetch_tensormap(&tm_c);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
@@ -332,7 +347,39 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
           }
         }
       }
-      if (ok && row_ok) {
+      bool stored = false;
+      if constexpr (!GROUPED) {
+        if (ok && p.tma_store) {
+          // The warp's 32 x EC block leaves in pieces of 32 rows x 128 bytes: written
+          // to shared memory in the 128-byte swizzle (conflict-free: lanes 0-7 hit eight
+          // different 16-byte columns), then one TMA store, which clips rows and columns
+          // outside the matrix. The next tile's K loop starts while the store drains.
+          constexpr int kPieceCols = 128 / static_cast<int>(sizeof(OutT));
+          constexpr int kChunkCols = 16 / static_cast<int>(sizeof(OutT));
+          const uint32_t my_stage = staging + (warp - 4) * C::kStoreStageBytes;
+          const int store_row = tc.row0 + quarter * 32;
+#pragma unroll
+          for (int pc = 0; pc < EC / kPieceCols; ++pc) {
+            const int pcol = col0 + pc * kPieceCols;
+            if (pcol >= p.n || store_row >= p.m) break;   // warp-uniform
+            if (lane == 0) bulk_wait_group_read_all();     // the previous piece has left the buffer
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint4 w = pack_16_bytes<OutT>(acc, pc * kPieceCols + j * kChunkCols);
+              st_shared_v4(my_stage + lane * 128 + ((j ^ (lane & 7)) << 4), w.x, w.y, w.z, w.w);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tm_c, my_stage, pcol, store_row);
+              bulk_commit_group();
+            }
+          }
+          stored = true;
+        }
+      }
+      if (ok && row_ok && !stored) {
         OutT* dst = out + static_cast<size_t>(row) * p.n + col0;
 #pragma unroll
         for (int c = 0; c < EC / 16; ++c) {
@@ -347,6 +394,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
         }
       }
     }
+    if (lane == 0) bulk_wait_group_all();   // shared memory must outlive the stores that read it
   } else {
     // warps 2 and 3 only complete warpgroup 0
     if constexpr (C::kRebalanceRegs) setmaxnreg_dec<C::kRegsIssue>();
@@ -376,7 +424,7 @@ bool encode_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dim
 }
 
 template <int BN, bool NT, bool GROUPED, typename OutT>
-ks_status_t launch_one(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUtensorMap& tm_b, const Params& p,
+ks_status_t launch_one(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUtensorMap& tm_b, Params p,
                        int grid, cudaStream_t stream) {
   using C = Cfg<BN>;
   auto kernel = fp8_blockwise_umma_kernel<BN, NT, GROUPED, OutT>;
@@ -387,12 +435,26 @@ ks_status_t launch_one(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUte
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+      cudaError_t e =
+          cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes(GROUPED));
       if (e != cudaSuccess) return cuda_status(e, a.where);
       attr_done[dev] = true;
     }
   }
-  kernel<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tm_a, tm_b, p);
+  // Output tensor map for the TMA-store epilogue (dense problems whose rows keep
+  // 16-byte alignment); otherwise the kernel stores from registers.
+  CUtensorMap tm_c = tm_a;
+  p.tma_store = 0;
+  if (!GROUPED && p.vec_store) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m)};
+    const uint64_t str[1] = {static_cast<uint64_t>(a.n) * sizeof(OutT)};
+    const uint32_t box[2] = {static_cast<uint32_t>(128 / sizeof(OutT)), 32u};
+    const CUtensorMapDataType dt = std::is_same<OutT, float>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : std::is_same<OutT, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                       : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    if (tma_encode(&tm_c, dt, 2, a.out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) p.tma_store = 1;
+  }
+  kernel<<<grid, C::kThreads, C::smem_bytes(GROUPED), stream>>>(tm_a, tm_b, tm_c, p);
   return cuda_status(cudaGetLastError(), a.where);
 }
 

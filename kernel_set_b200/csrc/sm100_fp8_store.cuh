@@ -61,5 +61,35 @@ __device__ __forceinline__ void store_16<__half>(__half* dst, const float* v, bo
   }
 }
 
+// Packs the 16 bytes that follow output column `c` (a multiple of 16 / sizeof(OutT))
+// of a row held as float2 pairs: 8 outputs of a 2-byte type, 4 floats.
+template <typename OutT>
+__device__ __forceinline__ uint4 pack_16_bytes(const float2* acc, int c);
+template <>
+__device__ __forceinline__ uint4 pack_16_bytes<float>(const float2* acc, int c) {
+  const float2 a = acc[c / 2], b = acc[c / 2 + 1];
+  return make_uint4(__float_as_uint(a.x), __float_as_uint(a.y), __float_as_uint(b.x), __float_as_uint(b.y));
+}
+template <>
+__device__ __forceinline__ uint4 pack_16_bytes<__nv_bfloat16>(const float2* acc, int c) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(acc[c / 2 + i].x, acc[c / 2 + i].y);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <>
+__device__ __forceinline__ uint4 pack_16_bytes<__half>(const float2* acc, int c) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = __floats2half2_rn(acc[c / 2 + i].x, acc[c / 2 + i].y);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 }  // namespace sm100
 }  // namespace ksb

@@ -380,6 +380,25 @@ __device__ __forceinline__ void tma_load_3d_elect(uint32_t smem_dst, const CUten
                : "memory");
 }
 
+// ---- TMA stores (shared -> global), tracked in per-thread bulk groups ---------------------
+// x (innermost coordinate) times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once the bulk groups of this thread have finished READING shared memory.
+__device__ __forceinline__ void bulk_wait_group_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// Returns once the bulk groups of this thread are complete.
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // ---- thread-block clusters and CTA pairs (cta_group::2) -------------------------------
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t r;
