@@ -42,6 +42,12 @@ namespace {
 #ifndef KSB_FP8_EPI_COLS
 #define KSB_FP8_EPI_COLS 128
 #endif
+#ifndef KSB_FP8_ACC_BUFS_128
+#define KSB_FP8_ACC_BUFS_128 4
+#endif
+#ifndef KSB_FP8_SCALE_GROUP
+#define KSB_FP8_SCALE_GROUP 2
+#endif
 #ifndef KSB_FP8_EPI_CHUNK
 #define KSB_FP8_EPI_CHUNK 16
 #endif
@@ -59,7 +65,7 @@ struct Cfg {
   // An epilogue warp owns 32 TMEM lanes x kEpiCols columns. Narrow slices keep
   // the per-K-block chain (wait, TMEM loads, FMAs, release) short: with 64
   // columns it is ~440 cycles, under the ~512 the MMAs of a K-block take.
-  static constexpr int kEpiCols = KSB_FP8_EPI_COLS;
+  static constexpr int kEpiCols = BN == 256 ? KSB_FP8_EPI_COLS : 64;
   static constexpr int kEpiWarps = (BN / kEpiCols) * 4;
   static constexpr int kThreads = 128 + kEpiWarps * 32;
   // Warpgroup 0 (TMA, MMA issue) hands registers to the epilogue warpgroups,
@@ -71,7 +77,12 @@ struct Cfg {
   // 128-column slices: 12 warps, 168 registers at launch -> 40 / 232.
   static constexpr int kRegsIssue = kEpiCols == 64 ? 32 : 40;
   static constexpr int kRegsEpi = kEpiCols == 64 ? 112 : 232;
-  static constexpr int kTmemCols = 2 * BN;
+  // Accumulator buffers in TMEM (512 columns): the MMA warp runs this many K-blocks
+  // ahead of the epilogue. A K-block's round trip (issue -> complete -> drained ->
+  // handed back) is about 1400 cycles whatever the tile width, so narrow tiles,
+  // whose MMAs are short, need more buffers in flight to keep the tensor core fed.
+  static constexpr int kAccBufs = BN == 256 ? 2 : KSB_FP8_ACC_BUFS_128;
+  static constexpr int kTmemCols = 512;
   // Dense problems stage the finished tile for TMA stores: 32 rows x 128 B per epilogue warp.
   static constexpr int kStoreStageBytes = 32 * 128;
   // ring + 1024 B alignment slack + barriers/flags, then either the store staging
@@ -151,12 +162,12 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
   const uint32_t staging = ring + C::kStages * C::kStageBytes;
   uint8_t* ctrl = smem_raw + (ring - raw_addr) + C::kStages * C::kStageBytes + kStagingBytes;
   const uint32_t ctrl_addr = staging + kStagingBytes;
-  // control block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem slot | abort flag
+  // control block: full[S] | empty[S] | tmem_full[B] | tmem_empty[B] | tmem slot | abort flag
   const uint32_t bar_full = ctrl_addr;
   const uint32_t bar_empty = ctrl_addr + 8 * C::kStages;
   const uint32_t bar_tfull = ctrl_addr + 16 * C::kStages;
-  const uint32_t bar_tempty = bar_tfull + 16;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * C::kStages + 32);
+  const uint32_t bar_tempty = bar_tfull + 8 * C::kAccBufs;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * C::kStages + 16 * C::kAccBufs);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   int* prefix = reinterpret_cast<int*>(ctrl + 256);
   int* offs = prefix + (kMaxExperts + 1);
@@ -170,7 +181,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < C::kAccBufs; ++b) {
       mbar_init(bar_tfull + 8 * b, 1);
       mbar_init(bar_tempty + 8 * b, C::kEpiWarps);
     }
@@ -239,8 +250,8 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
       for (int kb = 0; kb < p.nkb; ++kb, ++it) {
         const uint32_t s = it % C::kStages;
         const uint32_t ph = (it / C::kStages) & 1u;
-        const uint32_t buf = it & 1u;
-        const uint32_t aph = (it >> 1) & 1u;
+        const uint32_t buf = it % C::kAccBufs;
+        const uint32_t aph = (it / C::kAccBufs) & 1u;
         if (!mbar_wait(wctx, bar_tempty + 8 * buf, aph ^ 1u, 0x200u + buf)) { ok = false; break; }
         if (!mbar_wait(wctx, bar_full + 8 * s, ph, 0x300u + s)) { ok = false; break; }
         tc_fence_after_sync();
@@ -294,7 +305,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
       // Scales are fetched two K-blocks at a time, one group ahead of use: an
       // L2 round trip is longer than one K-block, so a load issued for the next
       // block alone would sit on the critical path.
-      constexpr int G = 2;
+      constexpr int G = KSB_FP8_SCALE_GROUP;
       constexpr int CW = KSB_FP8_EPI_CHUNK;  // TMEM columns per load
       float as_nxt[G], bs_nxt[G];
       auto fetch_scales = [&](int kb0) {
@@ -317,10 +328,12 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
         for (int j4 = 0; j4 < G; ++j4) {
           if (kb0 + j4 >= p.nkb) break;
           const float2 scale2 = make_float2(sc[j4], sc[j4]);
-          const uint32_t buf = it & 1u;
-          const uint32_t aph = (it >> 1) & 1u;
+          const uint32_t buf = it % C::kAccBufs;
+          const uint32_t aph = (it / C::kAccBufs) & 1u;
           ++it;
-          if (!mbar_wait(wctx, bar_tfull + 8 * buf, aph, 0x400u + buf)) { ok = false; break; }
+          // short suspend hint: these warps are the critical path of every K-block, and a
+          // waiter parked for the default period is resumed later than one that re-polls
+          if (!mbar_wait_hinted(wctx, bar_tfull + 8 * buf, aph, 0x400u + buf, 50u)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + slice * EC;
           uint32_t r0[CW], r1[CW];

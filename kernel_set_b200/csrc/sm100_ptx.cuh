@@ -123,6 +123,30 @@ __device__ __forceinline__ bool mbar_wait_long(const WaitCtx& ctx, uint32_t bar,
   }
 }
 
+// mbar_wait whose polls carry a suspend-time hint: the hardware parks the waiter for
+// about `hint_ns` at most before the next poll. For waits on a kernel's critical path.
+__device__ __forceinline__ bool mbar_wait_hinted(const WaitCtx& ctx, uint32_t bar, uint32_t parity, uint32_t code,
+                                                 uint32_t hint_ns) {
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try_wait_hint(bar, parity, hint_ns)) return true;
+  const unsigned long long t0 = global_ns();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait_hint(bar, parity, hint_ns)) return true;
+    if (*ctx.abort_flag != 0u) return false;
+    if (global_ns() - t0 > kWaitLimitNs) {
+      *ctx.abort_flag = 1u;
+      if (ctx.fault_word != nullptr) {
+        *reinterpret_cast<volatile unsigned int*>(ctx.fault_word) = 0x80000000u | code;
+        __threadfence_system();
+      }
+      return false;
+    }
+  }
+}
+
 __device__ __forceinline__ bool mbar_wait(const WaitCtx& ctx, uint32_t bar, uint32_t parity, uint32_t code) {
   // Fast path: plain polling, no timer and no shared-memory traffic besides the
   // barrier itself. Each failed try_wait may itself block for a short,
