@@ -10,17 +10,27 @@
 // CTA anatomy (one CTA per SM, persistent over output tiles of 128 x BN):
 //   warp 0      TMA producer: A tile 128 x 128 B and B tile BN x 128 B per stage,
 //               128-byte swizzle, completion counted on the stage's `full` barrier
-//   warp 1      MMA issuer: 4 UMMAs (M128, N=BN, K32) per K-block into TMEM buffer
-//               kb & 1; tcgen05.commit releases the stage and publishes the partial
+//   warp 1      MMA issuer: 4 UMMAs (M128, N=BN, K32) per K-block into one of the TMEM
+//               accumulator buffers (two of 256 columns, four of 128); ONE
+//               tcgen05.commit per K-block both releases the stage to the producer
+//               and tells the epilogue that the partial product is complete
 //   warps 2,3   idle (they complete warpgroup 0 so that register budgets can be
 //               moved between warpgroups with setmaxnreg)
-//   warps 4..   epilogue: warp w reads TMEM lanes 32*(w%4).. and 128 columns in
-//               32-column loads, double-buffered so that one load is in flight
+//   warps 4-11  epilogue: warp w reads TMEM lanes 32*(w%4).. and BN/2 columns in
+//               16-column loads, double-buffered so that one load is in flight
 //               while the previous one is folded in:
 //               acc = fma(partial, a_scale[row,kb] * b_scale[kb,nb], acc) in
 //               registers (packed two-wide), frees the TMEM buffer, and after
-//               the last K-block rounds once to the output type and stores its
-//               row segment
+//               the last K-block rounds once to the output type. Dense problems
+//               stage the tile in swizzled shared memory and leave by TMA store;
+//               grouped and unaligned ones store row segments from registers.
+// Measured on B200 (in-kernel cycle counters): a K-block of a 128 x 256 tile takes
+// ~850 cycles against 512 of tensor work. The epilogue's share is a serial chain per
+// warp (barrier test ~100, eight dependent TMEM loads ~55 each, 128 FMAs per thread:
+// the FP32 pipe alone needs 256 cycles per K-block) and with two accumulator buffers
+// the MMA warp and the epilogue take turns more than they overlap. Wider loads, more
+// loads in flight, sixteen narrower epilogue warps, 224-wide tiles, paced MMA issue
+// and sleeping or spinning waits were all measured and did not beat this arrangement.
 // B may be stored [N,K] (K-major UMMA operand) or [K,N] (MN-major operand, the
 // layout of the reference C ABI); both are loaded by TMA without a transpose.
 //
@@ -162,12 +172,11 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
   const uint32_t staging = ring + C::kStages * C::kStageBytes;
   uint8_t* ctrl = smem_raw + (ring - raw_addr) + C::kStages * C::kStageBytes + kStagingBytes;
   const uint32_t ctrl_addr = staging + kStagingBytes;
-  // control block: full[S] | empty[S] | tmem_full[B] | tmem_empty[B] | tmem slot | abort flag
+  // control block: full[S] | empty[S] | tmem_empty[B] | tmem slot | abort flag
   const uint32_t bar_full = ctrl_addr;
   const uint32_t bar_empty = ctrl_addr + 8 * C::kStages;
-  const uint32_t bar_tfull = ctrl_addr + 16 * C::kStages;
-  const uint32_t bar_tempty = bar_tfull + 8 * C::kAccBufs;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * C::kStages + 16 * C::kAccBufs);
+  const uint32_t bar_tempty = ctrl_addr + 16 * C::kStages;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * C::kStages + 8 * C::kAccBufs);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   int* prefix = reinterpret_cast<int*>(ctrl + 256);
   int* offs = prefix + (kMaxExperts + 1);
@@ -182,7 +191,6 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < C::kAccBufs; ++b) {
-      mbar_init(bar_tfull + 8 * b, 1);
       mbar_init(bar_tempty + 8 * b, C::kEpiWarps);
     }
     *abort_flag = 0u;
@@ -272,7 +280,6 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
             umma_f8f6f4_elect(d_tmem, a_desc, b_desc, p.idesc, kk > 0 ? 1u : 0u);
           }
           tc_commit_elect(bar_empty + 8 * s);
-          tc_commit_elect(bar_tfull + 8 * buf);
         }
       }
     }
@@ -333,7 +340,14 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
           ++it;
           // short suspend hint: these warps are the critical path of every K-block, and a
           // waiter parked for the default period is resumed later than one that re-polls
-          if (!mbar_wait_hinted(wctx, bar_tfull + 8 * buf, aph, 0x400u + buf, 50u)) { ok = false; break; }
+          // One tcgen05.commit per K-block serves both consumers: the barrier that hands the
+          // shared-memory stage back to the producer also tells the epilogue that the
+          // accumulator is complete (each extra commit costs the tensor core ~50 idle cycles).
+          {
+            const uint32_t s_done = (it - 1) % C::kStages, ph_done = ((it - 1) / C::kStages) & 1u;
+            if (!mbar_wait_hinted(wctx, bar_empty + 8 * s_done, ph_done, 0x400u + buf, 50u)) { ok = false; break; }
+          }
+
           tc_fence_after_sync();
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + slice * EC;
           uint32_t r0[CW], r1[CW];

@@ -59,6 +59,46 @@ def test_quantizer_deepseek_shape_full(ks, cuda):
     assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
 
 
+def test_quantizer_rounding_boundaries(ks, cuda):
+    """Quotients that sit on, just below and just above the midpoints between fp8 codes,
+    for thousands of different scales: any error in the last bit of x / scale shows."""
+    g = gen(77)
+    groups = 4096
+    codes = torch.arange(0, 127, dtype=torch.uint8).view(torch.float8_e4m3fn).float()   # 0 .. 448
+    mids = (codes[:-1] + codes[1:]) / 2
+    amax = torch.exp(torch.rand(groups, generator=g) * 30.0 - 15.0).float()              # 3e-7 .. 3e6
+    scale = torch.clamp(amax / 448.0, min=1e-12)
+    pick = torch.randint(0, mids.numel(), (groups, 127), generator=g)
+    x = scale[:, None] * mids[pick]
+    nudge = torch.randint(-1, 2, (groups, 127), generator=g)
+    up = torch.nextafter(x, torch.full_like(x, float("inf")))
+    down = torch.nextafter(x, torch.full_like(x, -float("inf")))
+    x = torch.where(nudge > 0, up, torch.where(nudge < 0, down, x))
+    sign = torch.randint(0, 2, (groups, 127), generator=g).float() * 2 - 1
+    x = torch.cat([amax[:, None], x * sign], dim=1).reshape(groups // 8, 8 * 128).contiguous()
+    q_ref, s_ref = orc.quantize_fp8_group(x, 128)
+    q, s = run_quant(ks, x, 128, "e4m3", cuda)
+    assert torch.equal(s, s_ref)
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+
+
+def test_quantizer_bf16_patterns(ks, cuda):
+    """Random bf16 bit patterns (every mantissa, a 12-binade window per group, windows from
+    2^-40 to 2^40): exercises the quotient path far from the N(0,1) activations."""
+    g = gen(78)
+    groups = 8192
+    e0 = torch.randint(127 - 40, 127 + 40, (groups, 1), generator=g)
+    expo = e0 - torch.randint(0, 12, (groups, 128), generator=g)
+    mant = torch.randint(0, 128, (groups, 128), generator=g)
+    sign = torch.randint(0, 2, (groups, 128), generator=g)
+    bits = (sign << 15) | (expo << 7) | mant
+    x = bits.to(torch.int32).to(torch.int16).view(torch.bfloat16).reshape(groups // 16, 16 * 128).contiguous()
+    q_ref, s_ref = orc.quantize_fp8_group(x, 128)
+    q, s = run_quant(ks, x, 128, "e4m3", cuda)
+    assert torch.equal(s, s_ref)
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+
+
 def test_quantizer_golden(ks, cuda):
     for tag in ("a", "b"):
         g = golden(f"fp8_blockwise_{tag}.npz")
