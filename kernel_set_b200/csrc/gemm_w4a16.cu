@@ -8,6 +8,16 @@
 #include "kernel_set/gemm.h"
 #include "sm100_w4a16.cuh"
 
+namespace {
+// KS_B200_W4A16_OPERAND=smem|tmem pins how decode shapes pass the dequantised weights to
+// the tensor core (tests and profiling only).
+int env_operand_path() {
+  const char* v = std::getenv("KS_B200_W4A16_OPERAND");
+  if (v == nullptr) return 0;
+  return v[0] == 's' ? 1 : (v[0] == 't' ? 2 : 0);
+}
+}  // namespace
+
 extern "C" ks_status_t ks_gemm_w4a16(void* c, const void* a, const void* b_packed, const void* scales,
                                      const void* zeros, const void* bias, int64_t m, int64_t n, int64_t k,
                                      int group_size, ks_dtype_t dtype, ks_stream_t stream) {
@@ -38,6 +48,7 @@ extern "C" ks_status_t ks_gemm_w4a16(void* c, const void* a, const void* b_packe
     sm100::W4A16Args args;
     args.c = c; args.a = a; args.b_packed = b_packed; args.scales = scales; args.zeros = zeros; args.bias = bias;
     args.m = m; args.n = n; args.k = k; args.group_size = gs; args.dtype = dtype;
+    args.operand_path = env_operand_path();
     if (path != 1 && sm100::w4a16_eligible(args)) return sm100::launch_w4a16(args, s);
     if (path == 2) KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE, "ks_gemm_w4a16: shape not eligible for the tcgen05 kernel");
   }
@@ -92,6 +103,7 @@ extern "C" ks_status_t ks_gemm_w4a16_static_scratch(void* c, const void* a, cons
   sm100::W4A16Args args;
   args.c = c; args.a = a; args.b_packed = b_packed; args.scales = scales; args.zeros = zeros; args.bias = bias;
   args.m = m; args.n = n; args.k = k; args.group_size = gs; args.dtype = dtype;
+    args.operand_path = env_operand_path();
   if (sm100::w4a16_eligible(args)) return sm100::launch_w4a16_static(args, s);
   const int64_t tiles_m = (m + general::kTM - 1) / general::kTM;
   const int64_t tiles_n = (n + general::kTN - 1) / general::kTN;

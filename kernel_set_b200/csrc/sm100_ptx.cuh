@@ -244,6 +244,18 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 
+// Lane i of the warp writes 16 consecutive 32-bit columns of TMEM lane (taddr.lane + i).
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// Returns once the tcgen05.st of this thread have been performed.
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // 32-column variant: lane i receives columns [col, col+32) of its TMEM lane.
 __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -371,6 +383,16 @@ __device__ __forceinline__ void umma_f16_elect(uint32_t d_tmem, uint64_t a_desc,
                "setp.ne.b32 p, %4, 0;\n\t"
                "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
                "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+// Same, with the A operand in tensor memory: 128 lanes (rows of A) x K/2 columns, a
+// 32-bit cell holding two consecutive 16-bit K elements (lower k in the low half).
+__device__ __forceinline__ void umma_f16_tmem_a_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                      uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t" KSB_ELECT_PROLOGUE
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+               "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
                : "memory");
 }
 __device__ __forceinline__ void tc_commit_elect(uint32_t bar) {

@@ -9,22 +9,42 @@
 //
 // The GEMM is transposed onto the tensor core: the weight's N dimension is the
 // UMMA M dimension (128 TMEM lanes), the tokens are the UMMA N dimension
-// (16..128 columns), so a CTA streams 128 weight columns x 128 k per step:
-//   warp 0        weight producer (TMA): packed tile [64 byte-rows x 128 columns]
-//                 = 8 KB straight from HBM plus the group's 128 scales and
-//                 zero-points (2 x 256 B), ten stages deep
-//   warp 2        activation producer (TMA): the K-slice [tokens x 128] (from L2)
-//   warps 4-11    dequantisation, two groups of four warps working on alternate
-//                 units (a thread then owns 128 weights of a unit, which
-//                 amortises the per-unit waits, fences and scale preparation;
-//                 two groups of eight warps measured slower):
-//                 8 packed bytes -> 16 weights per step:
-//                 nibble -> (128 + q) by byte-permute into a bf16 pattern,
-//                 minus (128 + zero), times scale, two packed 16-bit ops;
+// (16..128 columns), so a CTA streams 128 weight columns x 128 k per step ("unit").
+// Two ways of handing the dequantised weights (the A operand) to the tensor core:
+//
+// Tensor-memory operand (token tiles of at most 32 rows, K a multiple of 256; default there):
+//   warp 0        weight producer (TMA): boxes of two K-steps, [128 byte-rows x 128
+//                 columns] = 16 KB straight from HBM, eight stages. (A warp keeps only
+//                 about three TMA loads in flight whatever their size; 8 KB boxes cap a
+//                 single producer warp near 2.5 TB/s, 16 KB boxes near 4.5 TB/s.)
+//   warp 2        activation producer (TMA): one 3-D box per K-step (both 64-k swizzle
+//                 atoms of the K-slice [tokens x 128], from L2)
+//   warps 4-11    dequantisation, two groups of four warps on alternate units. A thread
+//                 owns ONE weight column (= one TMEM lane) and walks down its 64 packed
+//                 bytes: a byte holds the codes of k and k+1, exactly one 32-bit operand
+//                 cell; b * 0x1001 and one mask-or build the pair (magic + q), two packed
+//                 16-bit operations subtract (magic + zero) and apply the scale, and
+//                 tcgen05.st writes 16 cells at a time. Scales and zero-points are read
+//                 from global memory one unit ahead.
+//   warps 1, 3    MMA issuers: 4 x tcgen05.mma kind::f16 (M128, N=tokens, K16) each per
+//                 unit, A operand in tensor memory, into disjoint accumulators
+// Shared-memory operand (everything else, or KS_B200_W4A16_OPERAND=smem):
+//   warp 0        weight producer: packed tile [64 byte-rows x 128 columns] = 8 KB plus the
+//                 group's 128 scales and zero-points (2 x 256 B) per unit
+//   warp 2        activation producer (two 2-D boxes per unit)
+//   warps 4-11    dequantisation: a thread owns 8 columns x 16 k of a unit, 8 packed bytes
+//                 -> 16 weights per step by byte-permute into the (magic + q) pattern,
 //                 written as the MN-major, 128-byte-swizzled UMMA A operand
-//   warps 1, 3    MMA issuers: 4 x tcgen05.mma kind::f16 (M128, N=tokens, K16)
-//                 each per step, into disjoint TMEM accumulators
+//   warps 1, 3    MMA issuers, both operands from shared memory
+// Both:
 //   warps 12-15   epilogue: TMEM -> registers -> C, or -> an fp32 partial slot
+// Measured on B200, decode shapes: both arrangements take ~39 us for K=4096, N=28672
+// (~1000 cycles per unit against ~300 at the HBM rate). The shared-memory operand moves
+// 64 KB per unit through shared memory (~650 cycles at 128 B/clk); the tensor-memory
+// operand is bounded by tcgen05.st, which sustains only ~20 B/clk per scheduler whatever
+// the store width (~400 cycles per unit), and by its per-unit chain of waits. Processing
+// whole two-K-step boxes per iteration measured slower (48 us: two operand stages are too
+// few), as did sixteen dequantisation warps.
 // Work is cut stream-K style: the (column tile, K-step) units are dealt to the
 // CTAs in equal contiguous runs, so every SM streams the same number of bytes
 // whatever N is. A column tile whose K range is shared by several CTAs is
@@ -56,19 +76,33 @@ constexpr int kThreads = 512;
 constexpr int kDeqWarps = 8;       // two groups of four; a group takes every other unit
 constexpr int kDeqGroupWarps = 4;
 
-template <int MTMAX>
+// TA: the dequantised weights are handed to the tensor core through tensor memory
+// (tcgen05.st, A operand in TMEM) instead of shared memory. Decode shapes only
+// (MTMAX == 32): the accumulators of wider token tiles need all 512 TMEM columns.
+template <int MTMAX, bool TA>
 struct Cfg {
-  static constexpr int kRawStages = MTMAX <= 32 ? 9 : 6;
-  static constexpr int kActStages = MTMAX <= 32 ? 4 : 3;
-  static constexpr int kDeqStages = MTMAX <= 32 ? 3 : 2;
+  static_assert(!TA || MTMAX <= 32, "the TMEM operand path is built for token tiles of at most 32 rows");
+  // TA: a stage is one TMA box of two K-steps (16 KB); scales and zero-points do not
+  // travel through it. A warp keeps only about three TMA loads in flight, so the box
+  // has to be large for one producer warp to cover HBM latency.
+  static constexpr int kRawStages = TA ? 8 : (MTMAX <= 32 ? 9 : 6);
+  static constexpr int kRawStageBytes = TA ? 2 * kRawBytes : kRawStage;
+  static constexpr int kActStages = TA ? 8 : (MTMAX <= 32 ? 4 : 3);
+  static constexpr int kDeqStages = TA ? 4 : (MTMAX <= 32 ? 3 : 2);
+  // shared memory per dequantised stage; with TA a stage is 64 TMEM columns instead
+  static constexpr int kDeqSmem = TA ? 0 : kDeqBytes;
+  static constexpr int kDeqTmemCols = kStepK / 2;
   // Consecutive K=16 instructions of a step go to different TMEM accumulators:
   // an instruction that accumulates into the result of the previous one waits
   // for it, and with 16..32 token columns that latency, not throughput, would
   // set the pace. The epilogue adds the accumulators up.
-  static constexpr int kAccs = MTMAX <= 32 ? 8 : 2;
-  static constexpr int kTmemCols = 2 * kAccs * MTMAX;  // two segment buffers
+  static constexpr int kAccs = TA ? 4 : (MTMAX <= 32 ? 8 : 2);
+  static constexpr int kAccCols = 2 * kAccs * MTMAX;   // two segment buffers
+  static constexpr int kTmemCols = TA ? 512 : kAccCols;
+  static constexpr int kOperandCol0 = kAccCols;         // TA: first column of the operand ring
+  static_assert(!TA || kAccCols + kDeqStages * kDeqTmemCols <= 512, "TMEM holds 512 columns");
   static constexpr int kActStage = MTMAX * kStepK * 2;  // bytes reserved per activation stage
-  static constexpr int kRing = kDeqStages * kDeqBytes + kActStages * kActStage + kRawStages * kRawStage;
+  static constexpr int kRing = kDeqStages * kDeqSmem + kActStages * kActStage + kRawStages * kRawStageBytes;
   static constexpr int kNumBars = 2 * kRawStages + 2 * kActStages + 2 * kDeqStages + 4;
   static constexpr int kSmemBytes = kRing + 1024 + 512;
 };
@@ -76,6 +110,8 @@ struct Cfg {
 struct Params {
   void* c;
   const void* bias;
+  const void* scales;       // read directly by the tensor-memory path
+  const void* zeros;
   float* slots;             // [tiles][max_parts][mt][128] fp32 partials
   unsigned int* counters;   // [tiles]
   unsigned int* fault_word;
@@ -130,12 +166,12 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-template <typename T, int MTMAX>
+template <typename T, int MTMAX, bool TA>
 __global__ void __launch_bounds__(kThreads, 1)
 w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
                   const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_a,
                   const Params p) {
-  using C = Cfg<MTMAX>;
+  using C = Cfg<MTMAX, TA>;
   using P16 = Pack16<T>;
   using V2 = typename P16::V2;
   extern __shared__ uint8_t smem_raw[];
@@ -144,9 +180,9 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   uint8_t* base_ptr = smem_raw + (base - raw_addr);
   // ring: dequantised operand stages | activation stages | raw stages | barriers
   const uint32_t deq_base = base;
-  const uint32_t act_base = deq_base + C::kDeqStages * kDeqBytes;
+  const uint32_t act_base = deq_base + C::kDeqStages * C::kDeqSmem;
   const uint32_t rawst_base = act_base + C::kActStages * C::kActStage;
-  const uint32_t bar_base = rawst_base + C::kRawStages * kRawStage;
+  const uint32_t bar_base = rawst_base + C::kRawStages * C::kRawStageBytes;
   uint8_t* deq_ptr = base_ptr;
   uint8_t* rawst_ptr = base_ptr + (rawst_base - base);
   uint8_t* ctrl_ptr = base_ptr + (bar_base - base);
@@ -169,7 +205,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kRawStages; ++s) {
       mbar_init(bar_raw_full + 8 * s, 1);
-      mbar_init(bar_raw_empty + 8 * s, kDeqGroupWarps);
+      mbar_init(bar_raw_empty + 8 * s, TA ? kDeqWarps : kDeqGroupWarps);
     }
     for (int s = 0; s < C::kActStages; ++s) {
       mbar_init(bar_act_full + 8 * s, 1);
@@ -219,6 +255,23 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 
   if (warp == 0) {
     // ------------------------- weight producer (TMA) -------------------------
+    if constexpr (TA) {
+      // boxes of two K-steps; k_steps is even here, so a box never straddles two column
+      // tiles, and with a single token tile u indexes (tile, step) directly
+      const long long b_end = (u_end + 1) >> 1;
+      uint32_t itb = 0;
+      // (tile, step) advance with the loop: a 64-bit division per box would cost hundreds of cycles
+      int tile = static_cast<int>((u_begin & ~1ll) / p.k_steps);
+      int step = static_cast<int>((u_begin & ~1ll) - static_cast<long long>(tile) * p.k_steps);
+      for (long long b = u_begin >> 1; b < b_end; ++b, ++itb, step += 2) {
+        if (step >= p.k_steps) { step -= p.k_steps; ++tile; }
+        const uint32_t sr = itb % C::kRawStages, pr = (itb / C::kRawStages) & 1u;
+        if (!mbar_wait(wctx, bar_raw_empty + 8 * sr, pr ^ 1u, 0x100u + sr)) break;
+        const uint32_t full = bar_raw_full + 8 * sr;
+        mbar_arrive_expect_tx_elect(full, 2 * kRawBytes);
+        tma_load_2d_elect(rawst_base + sr * C::kRawStageBytes, &tm_w, full, tile * kTileN, step * (kStepK / 2));
+      }
+    } else {
     uint32_t it = 0;
     for (long long u = u_begin; u < u_end; ++u, ++it) {
       const long long ul = u % units;
@@ -235,21 +288,28 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         if (p.has_zeros) tma_load_2d_elect(dst + kRawBytes + 256, &tm_z, full, tile * kTileN, step / p.gs_steps);
       }
     }
+    }
   } else if (warp == 2) {
     // ----------------------- activation producer (TMA) -----------------------
     uint32_t it = 0;
-    for (long long u = u_begin; u < u_end; ++u, ++it) {
-      const int mtile = static_cast<int>(u / units);
-      const long long ul = u - static_cast<long long>(mtile) * units;
-      const int step = static_cast<int>(ul % p.k_steps);
+    int mtile = static_cast<int>(u_begin / units);
+    int step = static_cast<int>((u_begin - static_cast<long long>(mtile) * units) % p.k_steps);
+    long long next_mtile_at = (static_cast<long long>(mtile) + 1) * units;
+    for (long long u = u_begin; u < u_end; ++u, ++it, step = (step + 1 == p.k_steps) ? 0 : step + 1) {
+      if (u == next_mtile_at) { ++mtile; next_mtile_at += units; }
       const uint32_t sa = it % C::kActStages, pa = (it / C::kActStages) & 1u;
       if (!mbar_wait(wctx, bar_act_empty + 8 * sa, pa ^ 1u, 0x180u + sa)) break;
       {
         const uint32_t full = bar_act_full + 8 * sa;
         const uint32_t dst = act_base + sa * C::kActStage;
         mbar_arrive_expect_tx_elect(full, act_tx);
-        tma_load_2d_elect(dst, &tm_a, full, step * kStepK, mtile * p.mt);
-        tma_load_2d_elect(dst + p.mt * 128, &tm_a, full, step * kStepK + 64, mtile * p.mt);
+        if constexpr (TA) {
+          // one load for both 64-k atoms: the map views A as [K/64][M][64]
+          tma_load_3d_elect(dst, &tm_a, full, 0, mtile * p.mt, step * 2);
+        } else {
+          tma_load_2d_elect(dst, &tm_a, full, step * kStepK, mtile * p.mt);
+          tma_load_2d_elect(dst + p.mt * 128, &tm_a, full, step * kStepK + 64, mtile * p.mt);
+        }
       }
     }
   } else if (warp == 1 || warp == 3) {
@@ -274,7 +334,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         tc_fence_after_sync();
         {
           // all 32 lanes run this code; each instruction elects its one issuing lane
-          const uint32_t w_src = deq_base + sd * kDeqBytes;
+          const uint32_t w_src = deq_base + sd * C::kDeqSmem;
           const uint32_t a_src = act_base + sa * C::kActStage;
           const uint32_t d_tmem = tmem_base + buf * (C::kAccs * MTMAX);
 #pragma unroll
@@ -283,10 +343,17 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             // Weights: MN-major, 64-column atoms 16 KB apart, 8-k groups 1024 B
             // apart, 16 k = 2048 B per instruction. Tokens: K-major, two 64-k
             // atoms of mt rows, 32 B per instruction inside an atom.
-            const uint64_t w_desc = umma_smem_desc_sw128(w_src + kk * 2048, 16384, 1024);
             const uint64_t a_desc = umma_smem_desc_sw128(a_src + (kk >> 2) * (p.mt * 128) + (kk & 3) * 32, 16, 1024);
-            umma_f16_elect(d_tmem + (mma_half * kHalfAccs + (kq % kHalfAccs)) * MTMAX, w_desc, a_desc, p.idesc,
-                           (seg_first && kq < kHalfAccs) ? 0u : 1u);
+            const uint32_t d_acc = d_tmem + (mma_half * kHalfAccs + (kq % kHalfAccs)) * MTMAX;
+            const uint32_t first = (seg_first && kq < kHalfAccs) ? 0u : 1u;
+            if constexpr (TA) {
+              // weights from tensor memory: 16 k = 8 columns of the stage
+              const uint32_t w_tmem = tmem_base + C::kOperandCol0 + sd * C::kDeqTmemCols + kk * 8;
+              umma_f16_tmem_a_elect(d_acc, w_tmem, a_desc, p.idesc, first);
+            } else {
+              const uint64_t w_desc = umma_smem_desc_sw128(w_src + kk * 2048, 16384, 1024);
+              umma_f16_elect(d_acc, w_desc, a_desc, p.idesc, first);
+            }
           }
           tc_commit_elect(bar_deq_empty + 8 * sd);
           tc_commit_elect(bar_act_empty + 8 * sa);
@@ -304,7 +371,94 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const uint32_t atom_off = (oct >> 3) * 16384u;
     const uint32_t chunk = oct & 7;
     const V2 magic2 = P16::splat(P16::kMagic);
-    {
+    if constexpr (TA) {
+      // A thread owns one weight column (= one TMEM lane; warp w may only touch the lane
+      // quarter w % 4) and walks down its 64 packed bytes. A byte holds the codes of k and
+      // k+1, which is exactly one 32-bit operand cell: b * 0x1001 puts the low nibble at bit
+      // 0 and the high nibble at bit 16, one mask-and-or makes the pair (magic + q), and
+      // two packed operations subtract (magic + zero) and apply the scale.
+      const int quarter = warp & 3;
+      const int n_local = quarter * 32 + lane;
+      constexpr uint32_t kMagic2 = P16::kMagicBytes & 0xFF00FF00u;
+      // Group g owns the units of odd/even K-step g, i.e. half g of every box. Scales and
+      // zero-points come straight from global memory, fetched one unit ahead.
+      const unsigned short* gscales = static_cast<const unsigned short*>(p.scales);
+      const unsigned short* gzeros = static_cast<const unsigned short*>(p.zeros);
+      // (tile, step) of the unit whose scale is fetched next; it advances by two K-steps
+      // per fetch without any division (k_steps is even, so the parity of step is fixed)
+      const long long u_first = ((u_begin & 1) == group) ? u_begin : u_begin + 1;
+      int f_tile = static_cast<int>(u_first / p.k_steps);
+      int f_step = static_cast<int>(u_first - static_cast<long long>(f_tile) * p.k_steps);
+      int f_row = f_step / p.gs_steps, f_in_row = f_step - f_row * p.gs_steps;
+      auto fetch_sz = [&](uint32_t* s_out, uint32_t* z_out) {
+        const int n = f_tile * kTileN + n_local;
+        const size_t idx = static_cast<size_t>(f_row) * p.n + n;
+        const bool n_ok = n < p.n;
+        *s_out = n_ok ? __ldg(gscales + idx) : 0u;
+        *z_out = (n_ok && p.has_zeros) ? __ldg(gzeros + idx) : 0u;
+        f_step += 2;
+        f_in_row += 2;
+        if (f_step >= p.k_steps) { f_step -= p.k_steps; ++f_tile; f_row = 0; f_in_row = f_step; }
+        while (f_in_row >= p.gs_steps) { f_in_row -= p.gs_steps; ++f_row; }
+      };
+      const long long b_begin = u_begin >> 1, b_end = (u_end + 1) >> 1;
+      uint32_t s_next = 0u, z_next = 0u;
+      if (u_first < u_end) fetch_sz(&s_next, &z_next);
+      for (long long b = b_begin; b < b_end; ++b) {
+        const uint32_t itb = static_cast<uint32_t>(b - b_begin);
+        const uint32_t sr = itb % C::kRawStages, pr = (itb / C::kRawStages) & 1u;
+        const long long u = (b << 1) + group;
+        if (u < u_begin || u >= u_end) {
+          // the other half of this box belongs to a neighbouring CTA's run
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_raw_empty + 8 * sr);
+          continue;
+        }
+        const uint32_t it = static_cast<uint32_t>(u - u_begin);
+        const uint32_t sd = it % C::kDeqStages, pd = (it / C::kDeqStages) & 1u;
+        const uint32_t s16 = s_next, z16 = z_next;
+        if (u + 2 < u_end) fetch_sz(&s_next, &z_next);
+        if (!mbar_wait(wctx, bar_raw_full + 8 * sr, pr, 0x400u + sr)) break;
+        const uint8_t* col = rawst_ptr + sr * C::kRawStageBytes + group * kRawBytes + n_local;
+        const V2 sc = P16::from_bits(s16 | (s16 << 16));
+        const uint32_t zw = z16 | (z16 << 16);
+        const V2 zz = __hadd2(P16::from_bits(zw), magic2);
+        // (magic + zero) exact and |q - zero| exact: non-negative integer zero-points up to kMaxZero
+        const uint32_t back = P16::bits(__hsub2(zz, magic2));
+        const bool simple = ((back ^ zw) | (zw & 0x80008000u)) == 0u && z16 <= P16::kMaxZeroBits;
+        if (!mbar_wait(wctx, bar_deq_empty + 8 * sd, pd ^ 1u, 0x480u + sd)) break;
+        const uint32_t t_dst = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + C::kOperandCol0 +
+                               sd * C::kDeqTmemCols;
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t cells[16];
+          if (simple) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t b = col[(c4 * 16 + j) * kTileN];
+              const uint32_t x = ((b * 0x1001u) & 0x000F000Fu) | kMagic2;
+              cells[j] = P16::bits(__hmul2(__hsub2(P16::from_bits(x), zz), sc));
+            }
+          } else {
+            // zero-points that are not small integers: the fp32 statement, verbatim
+            const float z0 = P16::lo(P16::from_bits(zw)), s0 = P16::lo(sc);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t b = col[(c4 * 16 + j) * kTileN];
+              cells[j] = P16::bits(P16::make(__fmul_rn(__fsub_rn(static_cast<float>(b & 15u), z0), s0),
+                                             __fmul_rn(__fsub_rn(static_cast<float>(b >> 4), z0), s0)));
+            }
+          }
+          tmem_st(t_dst + c4 * 16, cells);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_raw_empty + 8 * sr);   // every byte of the packed stage has been read
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_deq_full + 8 * sd);
+      }
+    } else {
       for (long long u = u_begin + group; u < u_end; u += 2) {
         const uint32_t it = static_cast<uint32_t>(u - u_begin);
         const uint32_t sr = it % C::kRawStages, pr = (it / C::kRawStages) & 1u;
@@ -502,11 +656,11 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   }
 }
 
-template <typename T, int MTMAX>
+template <typename T, int MTMAX, bool TA>
 ks_status_t launch_t(const W4A16Args& a, const CUtensorMap& tm_w, const CUtensorMap& tm_s, const CUtensorMap& tm_z,
                      const CUtensorMap& tm_a, const Params& p, int grid, cudaStream_t stream) {
-  using C = Cfg<MTMAX>;
-  auto kernel = w4a16_umma_kernel<T, MTMAX>;
+  using C = Cfg<MTMAX, TA>;
+  auto kernel = w4a16_umma_kernel<T, MTMAX, TA>;
   static std::mutex mu;
   static bool attr_done[64] = {};
   int dev = 0;
@@ -568,11 +722,14 @@ ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, uint8_t* scratc
             max_parts = g.max_parts;
   const size_t counter_bytes = g.counter_bytes;
   const CUtensorMapDataType dt16 = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  // Decode shapes hand the weights over in tensor memory unless told otherwise; that path
+  // loads the packed weight two K-steps at a time.
+  const bool tmem_operand = mtmax == 32 && a.operand_path != 1 && (k_steps % 2 == 0);
   CUtensorMap tm_w, tm_s, tm_z, tm_a;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k / 2)};
     const uint64_t str[1] = {static_cast<uint64_t>(a.n)};
-    const uint32_t box[2] = {static_cast<uint32_t>(kTileN), static_cast<uint32_t>(kStepK / 2)};
+    const uint32_t box[2] = {static_cast<uint32_t>(kTileN), static_cast<uint32_t>(tmem_operand ? kStepK : kStepK / 2)};
     if (!tma_encode(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.b_packed, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE))
       KSB_FAIL(KS_ERROR_INTERNAL, "ks_gemm_w4a16: tensor map for the packed weight rejected");
   }
@@ -586,7 +743,14 @@ ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, uint8_t* scratc
                     CU_TENSOR_MAP_SWIZZLE_NONE))
       KSB_FAIL(KS_ERROR_INTERNAL, "ks_gemm_w4a16: tensor map for the zero-points rejected");
   }
-  {
+  if (tmem_operand) {
+    // A[M,K] seen as [K/64][M][64]: one box brings both 64-k swizzle atoms of a K-step
+    const uint64_t dims[3] = {64u, static_cast<uint64_t>(a.m), static_cast<uint64_t>(a.k / 64)};
+    const uint64_t str[2] = {static_cast<uint64_t>(a.k) * 2, 128u};
+    const uint32_t box[3] = {64u, static_cast<uint32_t>(mt), 2u};
+    if (!tma_encode(&tm_a, dt16, 3, a.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      KSB_FAIL(KS_ERROR_INTERNAL, "ks_gemm_w4a16: tensor map for the activations rejected");
+  } else {
     const uint64_t dims[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.m)};
     const uint64_t str[1] = {static_cast<uint64_t>(a.k) * 2};
     const uint32_t box[2] = {64u, static_cast<uint32_t>(mt)};
@@ -597,6 +761,8 @@ ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, uint8_t* scratc
   Params p;
   p.c = a.c;
   p.bias = a.bias;
+  p.scales = a.scales;
+  p.zeros = a.zeros;
   p.counters = reinterpret_cast<unsigned int*>(scratch);
   p.slots = reinterpret_cast<float*>(scratch + counter_bytes);
   p.fault_word = fault_word;
@@ -611,14 +777,17 @@ ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, uint8_t* scratc
   p.max_parts = max_parts;
   p.has_zeros = a.zeros != nullptr ? 1 : 0;
   const uint32_t fmt = bf16 ? 1u : 0u;
-  p.idesc = umma_instr_desc(fmt, fmt, 1u, 0u, 128u, static_cast<uint32_t>(mt));
+  // weights: MN-major in shared memory, K along the columns in tensor memory
+  p.idesc = umma_instr_desc(fmt, fmt, tmem_operand ? 0u : 1u, 0u, 128u, static_cast<uint32_t>(mt));
 
   if (bf16) {
-    return mtmax == 32 ? launch_t<__nv_bfloat16, 32>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream)
-                       : launch_t<__nv_bfloat16, 128>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream);
+    if (tmem_operand) return launch_t<__nv_bfloat16, 32, true>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream);
+    return mtmax == 32 ? launch_t<__nv_bfloat16, 32, false>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream)
+                       : launch_t<__nv_bfloat16, 128, false>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream);
   }
-  return mtmax == 32 ? launch_t<__half, 32>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream)
-                     : launch_t<__half, 128>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream);
+  if (tmem_operand) return launch_t<__half, 32, true>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream);
+  return mtmax == 32 ? launch_t<__half, 32, false>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream)
+                     : launch_t<__half, 128, false>(a, tm_w, tm_s, tm_z, tm_a, p, grid, stream);
 }
 
 }  // namespace
@@ -697,3 +866,4 @@ ks_status_t launch_w4a16_static(const W4A16Args& a, cudaStream_t stream) {
 
 }  // namespace sm100
 }  // namespace ksb
+

@@ -19,6 +19,9 @@ struct W4A16Args {
   int64_t m = 0, n = 0, k = 0;
   int group_size = 128;            // already resolved (> 0, divides k)
   ks_dtype_t dtype = KS_DTYPE_BF16;
+  // How decode shapes (at most 32 token rows) hand the dequantised weights to the tensor
+  // core: 0 = choose (tensor memory), 1 = shared memory, 2 = tensor memory.
+  int operand_path = 0;
 };
 
 // True when the tcgen05 kernel can take the problem: K and group_size multiples

@@ -232,6 +232,47 @@ def test_w4a16_tcgen05(ks, cuda, m, k, n, gs, dtype, zeros, bias):
     assert orc.rel_frobenius(out.cpu().float(), gen_out.cpu().float()) < 2e-3
 
 
+@pytest.mark.parametrize("operand", ["smem", "tmem"])
+@pytest.mark.parametrize("m,k,n,gs,dtype,zeros", [
+    (8, 1024, 512, 128, torch.bfloat16, "random"),
+    (32, 512, 208, 256, torch.float16, "eight"),      # ragged last column tile, two K-steps per group
+    (3, 768, 128, 128, torch.bfloat16, "fraction"),   # K = 6 steps, fp32 fallback for the zero-points
+    (17, 256, 384, 128, torch.bfloat16, None),
+])
+def test_w4a16_operand_paths(ks, cuda, operand, m, k, n, gs, dtype, zeros):
+    """Decode shapes through both ways of feeding the tensor core (shared-memory operand,
+    tensor-memory operand); both multiply the same rounded weights and differ by the
+    order of the fp32 sums only."""
+    g = gen(m * 3 + k + n)
+    a = torch.randn(m, k, generator=g).to(dtype)
+    codes = torch.randint(0, 16, (k, n), generator=g).to(torch.int32)
+    scales = (torch.randn(k // gs, n, generator=g).mul(0.02).abs() + 1e-3).to(dtype)
+    zp = {"eight": lambda: torch.full((k // gs, n), 8.0).to(dtype),
+          "random": lambda: torch.randint(0, 16, (k // gs, n), generator=g).to(dtype),
+          "fraction": lambda: (torch.rand(k // gs, n, generator=g) * 15).to(dtype),
+          None: lambda: None}[zeros]()
+    b_packed = orc.pack_int4_bytes(codes)
+    ref32 = orc.w4a16(a, b_packed, scales, zp, gs, None, out_dtype=None)
+    noise = accumulation_noise(a.float().abs(), orc.w4a16_weight(b_packed, scales, zp, gs).float().abs(), k)
+    old = os.environ.get("KS_B200_W4A16_OPERAND")
+    outs = {}
+    try:
+        for path in ("smem", "tmem"):
+            os.environ["KS_B200_W4A16_OPERAND"] = path
+            with w4_path("tcgen05"):
+                outs[path] = ks.dispatch.w4a16(a.to(cuda), b_packed.to(cuda), scales.to(cuda),
+                                               zp.to(cuda) if zp is not None else None, group_size=gs).cpu()
+            torch.cuda.synchronize()
+            ks.runtime.stream_synchronize(0)
+    finally:
+        if old is None:
+            os.environ.pop("KS_B200_W4A16_OPERAND", None)
+        else:
+            os.environ["KS_B200_W4A16_OPERAND"] = old
+    check_gemm(outs[operand], ref32, noise, f"w4a16 {operand} operand {m}x{n}x{k}")
+    assert orc.rel_frobenius(outs["smem"].float(), outs["tmem"].float()) < 2e-3
+
+
 def test_w4a16_golden(ks, cuda):
     for tag, dt in (("bf16", torch.bfloat16), ("f16", torch.float16)):
         g = golden(f"w4a16_{tag}.npz")
