@@ -72,9 +72,13 @@ constexpr int kStepK = 128;    // k per pipeline step (one scale group when gs %
 constexpr int kRawBytes = (kStepK / 2) * kTileN;      // 8192
 constexpr int kRawStage = kRawBytes + 2 * 256;        // + scales + zeros of the step
 constexpr int kDeqBytes = kStepK * kTileN * 2;        // 32768: dequantised UMMA operand
-constexpr int kThreads = 512;
-constexpr int kDeqWarps = 8;       // two groups of four; a group takes every other unit
-constexpr int kDeqGroupWarps = 4;
+constexpr int kDeqGroupWarps = 4;  // a group = one warp per TMEM lane quarter = one unit at a time
+#ifndef KSB_W4_TMEM_STAGES
+#define KSB_W4_TMEM_STAGES 4
+#endif
+#ifndef KSB_W4_TMEM_GROUPS
+#define KSB_W4_TMEM_GROUPS 4
+#endif
 
 // TA: the dequantised weights are handed to the tensor core through tensor memory
 // (tcgen05.st, A operand in TMEM) instead of shared memory. Decode shapes only
@@ -85,10 +89,18 @@ struct Cfg {
   // TA: a stage is one TMA box of two K-steps (16 KB); scales and zero-points do not
   // travel through it. A warp keeps only about three TMA loads in flight, so the box
   // has to be large for one producer warp to cover HBM latency.
+  // Dequantisation groups working on different units at the same time. The tensor-memory
+  // path is a chain of waits per unit (~1900 cycles per group); more groups in flight hide
+  // it until tcgen05.st bandwidth (~400 cycles per unit) becomes the limit.
+  static constexpr int kGroups = TA ? KSB_W4_TMEM_GROUPS : 2;
+  static constexpr int kDeqWarps = kGroups * kDeqGroupWarps;
+  static constexpr int kThreads = 128 + kDeqWarps * 32 + 128;   // producers/issuers, dequantisation, epilogue
   static constexpr int kRawStages = TA ? 8 : (MTMAX <= 32 ? 9 : 6);
   static constexpr int kRawStageBytes = TA ? 2 * kRawBytes : kRawStage;
   static constexpr int kActStages = TA ? 8 : (MTMAX <= 32 ? 4 : 3);
-  static constexpr int kDeqStages = TA ? 4 : (MTMAX <= 32 ? 3 : 2);
+  // TA: more operand stages than groups, so that a group can fill its next stage while the
+  // MMAs of its previous unit are still queued
+  static constexpr int kDeqStages = TA ? KSB_W4_TMEM_STAGES : (MTMAX <= 32 ? 3 : 2);
   // shared memory per dequantised stage; with TA a stage is 64 TMEM columns instead
   static constexpr int kDeqSmem = TA ? 0 : kDeqBytes;
   static constexpr int kDeqTmemCols = kStepK / 2;
@@ -96,7 +108,7 @@ struct Cfg {
   // an instruction that accumulates into the result of the previous one waits
   // for it, and with 16..32 token columns that latency, not throughput, would
   // set the pace. The epilogue adds the accumulators up.
-  static constexpr int kAccs = TA ? 4 : (MTMAX <= 32 ? 8 : 2);
+  static constexpr int kAccs = TA ? (KSB_W4_TMEM_STAGES > 4 ? 2 : 4) : (MTMAX <= 32 ? 8 : 2);   // TA: what the operand stages leave
   static constexpr int kAccCols = 2 * kAccs * MTMAX;   // two segment buffers
   static constexpr int kTmemCols = TA ? 512 : kAccCols;
   static constexpr int kOperandCol0 = kAccCols;         // TA: first column of the operand ring
@@ -167,7 +179,7 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
 }
 
 template <typename T, int MTMAX, bool TA>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((Cfg<MTMAX, TA>::kThreads), 1)
 w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
                   const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_a,
                   const Params p) {
@@ -205,15 +217,15 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kRawStages; ++s) {
       mbar_init(bar_raw_full + 8 * s, 1);
-      mbar_init(bar_raw_empty + 8 * s, TA ? kDeqWarps : kDeqGroupWarps);
+      mbar_init(bar_raw_empty + 8 * s, TA ? 2 * kDeqGroupWarps : kDeqGroupWarps);   // TA: both halves of a box
     }
     for (int s = 0; s < C::kActStages; ++s) {
       mbar_init(bar_act_full + 8 * s, 1);
-      mbar_init(bar_act_empty + 8 * s, 2);   // both MMA issuers commit
+      mbar_init(bar_act_empty + 8 * s, TA ? 1 : 2);   // TA: the issuer that owns the unit; else both
     }
     for (int s = 0; s < C::kDeqStages; ++s) {
       mbar_init(bar_deq_full + 8 * s, kDeqGroupWarps);
-      mbar_init(bar_deq_empty + 8 * s, 2);
+      mbar_init(bar_deq_empty + 8 * s, TA ? 1 : 2);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full + 8 * b, 2);
@@ -320,7 +332,50 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const int mma_half = warp == 3 ? 1 : 0;
     constexpr int kHalfAccs = C::kAccs / 2;
     uint32_t it = 0, seg = 0;
-    {
+    if constexpr (TA) {
+      // The two issuers take alternate units: per unit an issuer pays three barrier tests
+      // (~100 cycles each), eight MMAs (~55 each) and the commits; sharing every unit
+      // between both issuers made each of them pay the fixed part for every unit.
+      // Issuer h owns accumulators 2h and 2h+1 of the segment buffer and tells the epilogue
+      // "done" after its last unit of the segment; an issuer without a unit in a (one-unit)
+      // segment arrives without a commit, and the epilogue skips its accumulators.
+      int step = static_cast<int>(u_begin % p.k_steps);
+      uint32_t n_in_seg = 0;
+      for (long long u = u_begin; u < u_end; ++u, ++it, step = (step + 1 == p.k_steps) ? 0 : step + 1) {
+        const bool seg_first = (u == u_begin) || (step == 0);
+        const bool seg_last = (u + 1 == u_end) || (step == p.k_steps - 1);
+        const bool next_is_last = !seg_last && ((u + 2 == u_end) || (step + 1 == p.k_steps - 1));
+        const bool mine = static_cast<int>(it & 1u) == mma_half;
+        const uint32_t sd = it % C::kDeqStages, pd = (it / C::kDeqStages) & 1u;
+        const uint32_t sa = it % C::kActStages, pa = (it / C::kActStages) & 1u;
+        const uint32_t buf = seg & 1u, pacc = (seg >> 1) & 1u;
+        if (seg_first) n_in_seg = 0;
+        if (mine) {
+          if (n_in_seg == 0 && !mbar_wait(wctx, bar_acc_empty + 8 * buf, pacc ^ 1u, 0x200u + buf)) break;
+          if (!mbar_wait(wctx, bar_deq_full + 8 * sd, pd, 0x280u + sd)) break;
+          if (!mbar_wait(wctx, bar_act_full + 8 * sa, pa, 0x300u + sa)) break;
+          tc_fence_after_sync();
+          const uint32_t a_src = act_base + sa * C::kActStage;
+          const uint32_t d_tmem = tmem_base + buf * (C::kAccs * MTMAX);
+          const uint32_t w_stage = tmem_base + C::kOperandCol0 + sd * C::kDeqTmemCols;
+#pragma unroll
+          for (int kk = 0; kk < kStepK / 16; ++kk) {
+            // tokens: K-major, two 64-k atoms of mt rows, 32 B per instruction inside an atom;
+            // weights: 16 k = 8 columns of the operand stage in tensor memory
+            const uint64_t a_desc = umma_smem_desc_sw128(a_src + (kk >> 2) * (p.mt * 128) + (kk & 3) * 32, 16, 1024);
+            const uint32_t d_acc = d_tmem + (mma_half * kHalfAccs + (kk % kHalfAccs)) * MTMAX;
+            umma_f16_tmem_a_elect(d_acc, w_stage + kk * 8, a_desc, p.idesc, (n_in_seg == 0 && kk < kHalfAccs) ? 0u : 1u);
+          }
+          ++n_in_seg;
+          tc_commit_elect(bar_deq_empty + 8 * sd);
+          tc_commit_elect(bar_act_empty + 8 * sa);
+          if (seg_last || next_is_last) tc_commit_elect(bar_acc_full + 8 * buf);   // my last unit of the segment
+        } else if (seg_last && n_in_seg == 0) {
+          mbar_arrive_elect(bar_acc_full + 8 * buf);   // a one-unit segment that was not mine
+        }
+        if (seg_last) ++seg;
+      }
+    } else {
       int step = static_cast<int>(u_begin % p.k_steps);
       for (long long u = u_begin; u < u_end; ++u, ++it, step = (step + 1 == p.k_steps) ? 0 : step + 1) {
         const bool seg_first = (u == u_begin) || (step == 0);
@@ -346,14 +401,8 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             const uint64_t a_desc = umma_smem_desc_sw128(a_src + (kk >> 2) * (p.mt * 128) + (kk & 3) * 32, 16, 1024);
             const uint32_t d_acc = d_tmem + (mma_half * kHalfAccs + (kq % kHalfAccs)) * MTMAX;
             const uint32_t first = (seg_first && kq < kHalfAccs) ? 0u : 1u;
-            if constexpr (TA) {
-              // weights from tensor memory: 16 k = 8 columns of the stage
-              const uint32_t w_tmem = tmem_base + C::kOperandCol0 + sd * C::kDeqTmemCols + kk * 8;
-              umma_f16_tmem_a_elect(d_acc, w_tmem, a_desc, p.idesc, first);
-            } else {
-              const uint64_t w_desc = umma_smem_desc_sw128(w_src + kk * 2048, 16384, 1024);
-              umma_f16_elect(d_acc, w_desc, a_desc, p.idesc, first);
-            }
+            const uint64_t w_desc = umma_smem_desc_sw128(w_src + kk * 2048, 16384, 1024);
+            umma_f16_elect(d_acc, w_desc, a_desc, p.idesc, first);
           }
           tc_commit_elect(bar_deq_empty + 8 * sd);
           tc_commit_elect(bar_act_empty + 8 * sa);
@@ -362,9 +411,9 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         if (seg_last) ++seg;
       }
     }
-  } else if (warp >= 4 && warp < 4 + kDeqWarps) {
+  } else if (warp >= 4 && warp < 4 + C::kDeqWarps) {
     // ----------------------------- dequantisation -----------------------------
-    const int group = (warp - 4) >> 2;          // 0: even units of this CTA's run, 1: odd units
+    const int group = (warp - 4) >> 2;          // which units of this CTA's run: u % kGroups == group
     const int tt = (threadIdx.x - 128) & 127;   // thread inside its group
     const int oct = tt & 15;   // 8 weight columns: n_local = 8*oct .. 8*oct+7
     const int rg = tt >> 4;    // 8 packed byte-rows: k_local = 16*rg .. 16*rg+15
@@ -380,13 +429,20 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       const int quarter = warp & 3;
       const int n_local = quarter * 32 + lane;
       constexpr uint32_t kMagic2 = P16::kMagicBytes & 0xFF00FF00u;
-      // Group g owns the units of odd/even K-step g, i.e. half g of every box. Scales and
-      // zero-points come straight from global memory, fetched one unit ahead.
+      // Group g owns the units u with u % kGroups == g: K-step half (g & 1) of every box b
+      // with b % (kGroups / 2) == g >> 1. Scales and zero-points come straight from global
+      // memory, fetched one unit of the group ahead; (tile, step) of the unit being fetched
+      // advance without any 64-bit division (k_steps and kGroups are even, so the parity of
+      // step is fixed).
+      constexpr int kBoxStride = C::kGroups / 2;
+      const int half = group & 1;
       const unsigned short* gscales = static_cast<const unsigned short*>(p.scales);
       const unsigned short* gzeros = static_cast<const unsigned short*>(p.zeros);
-      // (tile, step) of the unit whose scale is fetched next; it advances by two K-steps
-      // per fetch without any division (k_steps is even, so the parity of step is fixed)
-      const long long u_first = ((u_begin & 1) == group) ? u_begin : u_begin + 1;
+      const long long b_begin = u_begin >> 1, b_end = (u_end + 1) >> 1;
+      long long b_first = b_begin;
+      while ((b_first % kBoxStride) != (group >> 1)) ++b_first;
+      long long u_first = (b_first << 1) + half;
+      if (u_first < u_begin) u_first += C::kGroups;
       int f_tile = static_cast<int>(u_first / p.k_steps);
       int f_step = static_cast<int>(u_first - static_cast<long long>(f_tile) * p.k_steps);
       int f_row = f_step / p.gs_steps, f_in_row = f_step - f_row * p.gs_steps;
@@ -396,20 +452,23 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const bool n_ok = n < p.n;
         *s_out = n_ok ? __ldg(gscales + idx) : 0u;
         *z_out = (n_ok && p.has_zeros) ? __ldg(gzeros + idx) : 0u;
-        f_step += 2;
-        f_in_row += 2;
-        if (f_step >= p.k_steps) { f_step -= p.k_steps; ++f_tile; f_row = 0; f_in_row = f_step; }
+        f_step += C::kGroups;
+        f_in_row += C::kGroups;
+        if (f_step >= p.k_steps) {
+          while (f_step >= p.k_steps) { f_step -= p.k_steps; ++f_tile; }
+          f_row = 0;
+          f_in_row = f_step;
+        }
         while (f_in_row >= p.gs_steps) { f_in_row -= p.gs_steps; ++f_row; }
       };
-      const long long b_begin = u_begin >> 1, b_end = (u_end + 1) >> 1;
       uint32_t s_next = 0u, z_next = 0u;
       if (u_first < u_end) fetch_sz(&s_next, &z_next);
-      for (long long b = b_begin; b < b_end; ++b) {
+      for (long long b = b_first; b < b_end; b += kBoxStride) {
         const uint32_t itb = static_cast<uint32_t>(b - b_begin);
         const uint32_t sr = itb % C::kRawStages, pr = (itb / C::kRawStages) & 1u;
-        const long long u = (b << 1) + group;
+        const long long u = (b << 1) + half;
         if (u < u_begin || u >= u_end) {
-          // the other half of this box belongs to a neighbouring CTA's run
+          // this half of the box belongs to a neighbouring CTA's run
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_raw_empty + 8 * sr);
           continue;
@@ -417,9 +476,9 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const uint32_t it = static_cast<uint32_t>(u - u_begin);
         const uint32_t sd = it % C::kDeqStages, pd = (it / C::kDeqStages) & 1u;
         const uint32_t s16 = s_next, z16 = z_next;
-        if (u + 2 < u_end) fetch_sz(&s_next, &z_next);
+        if (u + C::kGroups < u_end) fetch_sz(&s_next, &z_next);
         if (!mbar_wait(wctx, bar_raw_full + 8 * sr, pr, 0x400u + sr)) break;
-        const uint8_t* col = rawst_ptr + sr * C::kRawStageBytes + group * kRawBytes + n_local;
+        const uint8_t* col = rawst_ptr + sr * C::kRawStageBytes + half * kRawBytes + n_local;
         const V2 sc = P16::from_bits(s16 | (s16 << 16));
         const uint32_t zw = z16 | (z16 << 16);
         const V2 zz = __hadd2(P16::from_bits(zw), magic2);
@@ -542,11 +601,11 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         if (lane == 0) mbar_arrive(bar_deq_full + 8 * sd);
       }
     }
-  } else if (warp >= 4 + kDeqWarps) {
+  } else if (warp >= 4 + C::kDeqWarps) {
     // -------------------------------- epilogue --------------------------------
     const int quarter = warp & 3;
     const int n_local = quarter * 32 + lane;   // TMEM lane = weight column inside the tile
-    const int et = threadIdx.x - (128 + kDeqWarps * 32);
+    const int et = threadIdx.x - (128 + C::kDeqWarps * 32);
     T* c = static_cast<T*>(p.c);
     const T* bias = static_cast<const T*>(p.bias);
     uint32_t seg = 0;
@@ -561,6 +620,10 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const long long tile_end = u - step0 + p.k_steps;
         const long long seg_end = tile_end < u_end ? tile_end : u_end;
         const bool whole = (step0 == 0) && (seg_end == tile_end);
+        // TA: the MMA issuers take alternate units of the CTA's run; in a one-unit segment
+        // only one of them has written its accumulators
+        const bool issuer_has_units[2] = {(seg_end - u >= 2) || (((u - u_begin) & 1) == 0),
+                                          (seg_end - u >= 2) || (((u - u_begin) & 1) == 1)};
         const uint32_t buf = seg & 1u, pacc = (seg >> 1) & 1u;
         ++seg;
         u = seg_end;
@@ -583,6 +646,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           for (int j = 0; j < 16; ++j) v[j] = 0.f;
 #pragma unroll
           for (int acc = 0; acc < C::kAccs; ++acc) {
+            if (TA && !issuer_has_units[acc / (C::kAccs / 2)]) continue;   // stale accumulators
             uint32_t r[16];
             tmem_ld(taddr + acc * MTMAX + cc, r);
             tmem_wait_ld(r);
@@ -673,7 +737,7 @@ ks_status_t launch_t(const W4A16Args& a, const CUtensorMap& tm_w, const CUtensor
       attr_done[dev] = true;
     }
   }
-  kernel<<<grid, kThreads, C::kSmemBytes, stream>>>(tm_w, tm_s, tm_z, tm_a, p);
+  kernel<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tm_w, tm_s, tm_z, tm_a, p);
   return cuda_status(cudaGetLastError(), "ks_gemm_w4a16");
 }
 
