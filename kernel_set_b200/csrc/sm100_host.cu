@@ -31,7 +31,7 @@ struct Scratch {
   size_t bytes = 0;
 };
 std::mutex g_scratch_mutex;
-std::map<std::pair<int, cudaStream_t>, Scratch> g_scratch;
+std::map<std::pair<std::pair<int, cudaStream_t>, int>, Scratch> g_scratch;
 
 }  // namespace
 
@@ -55,14 +55,15 @@ bool tma_encode(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const voi
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-void* stream_scratch(cudaStream_t stream, size_t bytes) {
+void* stream_scratch(cudaStream_t stream, size_t bytes, int kind) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
   std::lock_guard<std::mutex> lock(g_scratch_mutex);
-  Scratch& s = g_scratch[std::make_pair(dev, stream)];
+  Scratch& s = g_scratch[std::make_pair(std::make_pair(dev, stream), kind)];
   if (s.bytes >= bytes && s.ptr != nullptr) return s.ptr;
-  size_t want = bytes < (size_t(1) << 20) ? (size_t(1) << 20) : bytes;
-  want = (want + 0xFFFFF) & ~size_t(0xFFFFF);
+  const size_t floor_bytes = kind == 0 ? (size_t(1) << 20) : (size_t(64) << 10);
+  size_t want = bytes < floor_bytes ? floor_bytes : bytes;
+  want = (want + 0xFFFF) & ~size_t(0xFFFF);
   void* fresh = nullptr;
   if (cudaMallocAsync(&fresh, want, stream) != cudaSuccess) {
     cudaGetLastError();

@@ -20,12 +20,13 @@ bool tma_available();
 bool tma_encode(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
                 const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle);
 
-// Library-owned scratch memory for the current device and the given stream,
-// at least `bytes` large and zero-filled when (re)allocated. The pointer stays
-// valid until a later call asks for more on the same (device, stream); growth
-// is stream-ordered (cudaMallocAsync / cudaFreeAsync), so work already queued
-// on the stream keeps its buffer. Returns NULL when the allocation fails.
-void* stream_scratch(cudaStream_t stream, size_t bytes);
+// Library-owned scratch memory for the current device, the given stream and the given
+// purpose (`kind`: buffers of different kinds never share memory), at least `bytes` large
+// and zero-filled when (re)allocated. The pointer stays valid until a later call asks for
+// more of the same kind on the same (device, stream); growth is stream-ordered
+// (cudaMallocAsync / cudaFreeAsync), so work already queued on the stream keeps its buffer.
+// Returns NULL when the allocation fails.
+void* stream_scratch(cudaStream_t stream, size_t bytes, int kind = 0);
 
 }  // namespace sm100
 }  // namespace ksb

@@ -123,6 +123,18 @@ __device__ __forceinline__ bool mbar_wait_long(const WaitCtx& ctx, uint32_t bar,
   }
 }
 
+// Waits for two barriers whose phases are usually both complete already: both are
+// tested before either result is used, so the two ~100-cycle round trips overlap.
+__device__ __forceinline__ bool mbar_wait_both(const WaitCtx& ctx, uint32_t bar_a, uint32_t parity_a, uint32_t code_a,
+                                               uint32_t bar_b, uint32_t parity_b, uint32_t code_b) {
+  const bool a = mbar_try_wait(bar_a, parity_a);
+  const bool b = mbar_try_wait(bar_b, parity_b);
+  if (a && b) return true;
+  if (!a && !mbar_wait(ctx, bar_a, parity_a, code_a)) return false;
+  if (!b && !mbar_wait(ctx, bar_b, parity_b, code_b)) return false;
+  return true;
+}
+
 // mbar_wait whose polls carry a suspend-time hint: the hardware parks the waiter for
 // about `hint_ns` at most before the next poll. For waits on a kernel's critical path.
 __device__ __forceinline__ bool mbar_wait_hinted(const WaitCtx& ctx, uint32_t bar, uint32_t parity, uint32_t code,

@@ -73,6 +73,14 @@ constexpr int kRawBytes = (kStepK / 2) * kTileN;      // 8192
 constexpr int kRawStage = kRawBytes + 2 * 256;        // + scales + zeros of the step
 constexpr int kDeqBytes = kStepK * kTileN * 2;        // 32768: dequantised UMMA operand
 constexpr int kDeqGroupWarps = 4;  // a group = one warp per TMEM lane quarter = one unit at a time
+// The numbers of operand stages and of activation stages must be multiples of the number
+// of issuers: an issuer's wait on a stage's `full` barrier is ordered after the stage's
+// previous use only because the same issuer consumed that use. (Three issuers with four
+// stages let an issuer pass a fresh barrier one phase early: intermittent bounded-wait
+// timeouts on the GPU, and a deadlock in the protocol model under tests/.)
+#ifndef KSB_W4_TMEM_ISSUERS
+#define KSB_W4_TMEM_ISSUERS 2
+#endif
 #ifndef KSB_W4_TMEM_STAGES
 #define KSB_W4_TMEM_STAGES 4
 #endif
@@ -94,7 +102,13 @@ struct Cfg {
   // it until tcgen05.st bandwidth (~400 cycles per unit) becomes the limit.
   static constexpr int kGroups = TA ? KSB_W4_TMEM_GROUPS : 2;
   static constexpr int kDeqWarps = kGroups * kDeqGroupWarps;
-  static constexpr int kThreads = 128 + kDeqWarps * 32 + 128;   // producers/issuers, dequantisation, epilogue
+  // MMA issuers: warps 1 and 3, plus (TA) extra warps after the epilogue warps. An issuer
+  // spends ~1000 cycles per unit it owns (barrier tests, eight MMAs, commits).
+  static constexpr int kIssuers = TA ? KSB_W4_TMEM_ISSUERS : 2;
+  static_assert(!TA || (KSB_W4_TMEM_STAGES % KSB_W4_TMEM_ISSUERS == 0 && 8 % KSB_W4_TMEM_ISSUERS == 0),
+                "stage counts must be multiples of the number of issuers");
+  static constexpr int kExtraIssuerWarp0 = 4 + kDeqWarps + 4;   // first warp index after the epilogue warps
+  static constexpr int kThreads = 128 + kDeqWarps * 32 + 128 + (kIssuers - 2) * 32;
   static constexpr int kRawStages = TA ? 8 : (MTMAX <= 32 ? 9 : 6);
   static constexpr int kRawStageBytes = TA ? 2 * kRawBytes : kRawStage;
   static constexpr int kActStages = TA ? 8 : (MTMAX <= 32 ? 4 : 3);
@@ -108,7 +122,9 @@ struct Cfg {
   // an instruction that accumulates into the result of the previous one waits
   // for it, and with 16..32 token columns that latency, not throughput, would
   // set the pace. The epilogue adds the accumulators up.
-  static constexpr int kAccs = TA ? (KSB_W4_TMEM_STAGES > 4 ? 2 : 4) : (MTMAX <= 32 ? 8 : 2);   // TA: what the operand stages leave
+  // TA: accumulators per issuer times issuers; the operand stages take the rest of TMEM
+  static constexpr int kAccsPerIssuer = (TA && (KSB_W4_TMEM_STAGES > 4 || KSB_W4_TMEM_ISSUERS > 2)) ? 1 : 2;
+  static constexpr int kAccs = TA ? kAccsPerIssuer * kIssuers : (MTMAX <= 32 ? 8 : 2);
   static constexpr int kAccCols = 2 * kAccs * MTMAX;   // two segment buffers
   static constexpr int kTmemCols = TA ? 512 : kAccCols;
   static constexpr int kOperandCol0 = kAccCols;         // TA: first column of the operand ring
@@ -228,7 +244,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       mbar_init(bar_deq_empty + 8 * s, TA ? 1 : 2);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(bar_acc_full + 8 * b, 2);
+      mbar_init(bar_acc_full + 8 * b, C::kIssuers);
       mbar_init(bar_acc_empty + 8 * b, 4);
     }
     *abort_flag = 0u;
@@ -324,36 +340,38 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         }
       }
     }
-  } else if (warp == 1 || warp == 3) {
+  } else if (warp == 1 || warp == 3 || (warp >= C::kExtraIssuerWarp0 && warp < C::kExtraIssuerWarp0 + C::kIssuers - 2)) {
     // ------------------------------ MMA issuers ------------------------------
     // Issuing one tcgen05.mma costs its thread ~55 cycles; eight per unit from one
     // thread would set the pace of the whole kernel. Two warps issue four each,
     // into disjoint accumulators (an accumulator must have a single issuer).
-    const int mma_half = warp == 3 ? 1 : 0;
-    constexpr int kHalfAccs = C::kAccs / 2;
+    const int mma_half = warp == 1 ? 0 : (warp == 3 ? 1 : 2 + (warp - C::kExtraIssuerWarp0));   // issuer index
+    constexpr int kHalfAccs = TA ? C::kAccsPerIssuer : C::kAccs / 2;
     uint32_t it = 0, seg = 0;
     if constexpr (TA) {
-      // The two issuers take alternate units: per unit an issuer pays three barrier tests
-      // (~100 cycles each), eight MMAs (~55 each) and the commits; sharing every unit
-      // between both issuers made each of them pay the fixed part for every unit.
-      // Issuer h owns accumulators 2h and 2h+1 of the segment buffer and tells the epilogue
-      // "done" after its last unit of the segment; an issuer without a unit in a (one-unit)
-      // segment arrives without a commit, and the epilogue skips its accumulators.
+      // The issuers take the units in turn (unit it -> issuer it % kIssuers): per unit an
+      // issuer pays its barrier tests (~100 cycles each), eight MMAs (~55 each) and the
+      // commits; sharing every unit between all issuers made each of them pay the fixed part
+      // for every unit. An issuer owns its accumulator(s) of the segment buffer and tells the
+      // epilogue "done" after its last unit of the segment; an issuer without a unit in a
+      // short segment arrives without a commit, and the epilogue skips its accumulators.
       int step = static_cast<int>(u_begin % p.k_steps);
       uint32_t n_in_seg = 0;
       for (long long u = u_begin; u < u_end; ++u, ++it, step = (step + 1 == p.k_steps) ? 0 : step + 1) {
         const bool seg_first = (u == u_begin) || (step == 0);
         const bool seg_last = (u + 1 == u_end) || (step == p.k_steps - 1);
-        const bool next_is_last = !seg_last && ((u + 2 == u_end) || (step + 1 == p.k_steps - 1));
-        const bool mine = static_cast<int>(it & 1u) == mma_half;
+        // last unit of this segment: end of the column tile or of this CTA's run
+        const long long tile_last = u - step + p.k_steps - 1;
+        const long long seg_last_u = tile_last < u_end - 1 ? tile_last : u_end - 1;
+        const bool mine = static_cast<int>(it % C::kIssuers) == mma_half;
+        const bool my_last = u + C::kIssuers > seg_last_u;   // no later unit of mine in this segment
         const uint32_t sd = it % C::kDeqStages, pd = (it / C::kDeqStages) & 1u;
         const uint32_t sa = it % C::kActStages, pa = (it / C::kActStages) & 1u;
         const uint32_t buf = seg & 1u, pacc = (seg >> 1) & 1u;
         if (seg_first) n_in_seg = 0;
         if (mine) {
           if (n_in_seg == 0 && !mbar_wait(wctx, bar_acc_empty + 8 * buf, pacc ^ 1u, 0x200u + buf)) break;
-          if (!mbar_wait(wctx, bar_deq_full + 8 * sd, pd, 0x280u + sd)) break;
-          if (!mbar_wait(wctx, bar_act_full + 8 * sa, pa, 0x300u + sa)) break;
+          if (!mbar_wait_both(wctx, bar_deq_full + 8 * sd, pd, 0x280u + sd, bar_act_full + 8 * sa, pa, 0x300u + sa)) break;
           tc_fence_after_sync();
           const uint32_t a_src = act_base + sa * C::kActStage;
           const uint32_t d_tmem = tmem_base + buf * (C::kAccs * MTMAX);
@@ -369,9 +387,13 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           ++n_in_seg;
           tc_commit_elect(bar_deq_empty + 8 * sd);
           tc_commit_elect(bar_act_empty + 8 * sa);
-          if (seg_last || next_is_last) tc_commit_elect(bar_acc_full + 8 * buf);   // my last unit of the segment
+          if (my_last) tc_commit_elect(bar_acc_full + 8 * buf);   // my last unit of the segment
         } else if (seg_last && n_in_seg == 0) {
-          mbar_arrive_elect(bar_acc_full + 8 * buf);   // a one-unit segment that was not mine
+          // A short segment without a unit of mine. Like an issuer with work, wait until the
+          // epilogue has drained this buffer's previous segment: otherwise this arrival could
+          // overtake my own (asynchronous) commit for that segment and complete its phase early.
+          if (!mbar_wait(wctx, bar_acc_empty + 8 * buf, pacc ^ 1u, 0x200u + buf)) break;
+          mbar_arrive_elect(bar_acc_full + 8 * buf);
         }
         if (seg_last) ++seg;
       }
@@ -477,7 +499,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const uint32_t sd = it % C::kDeqStages, pd = (it / C::kDeqStages) & 1u;
         const uint32_t s16 = s_next, z16 = z_next;
         if (u + C::kGroups < u_end) fetch_sz(&s_next, &z_next);
-        if (!mbar_wait(wctx, bar_raw_full + 8 * sr, pr, 0x400u + sr)) break;
+        if (!mbar_wait_both(wctx, bar_raw_full + 8 * sr, pr, 0x400u + sr, bar_deq_empty + 8 * sd, pd ^ 1u, 0x480u + sd)) break;
         const uint8_t* col = rawst_ptr + sr * C::kRawStageBytes + half * kRawBytes + n_local;
         const V2 sc = P16::from_bits(s16 | (s16 << 16));
         const uint32_t zw = z16 | (z16 << 16);
@@ -485,7 +507,6 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         // (magic + zero) exact and |q - zero| exact: non-negative integer zero-points up to kMaxZero
         const uint32_t back = P16::bits(__hsub2(zz, magic2));
         const bool simple = ((back ^ zw) | (zw & 0x80008000u)) == 0u && z16 <= P16::kMaxZeroBits;
-        if (!mbar_wait(wctx, bar_deq_empty + 8 * sd, pd ^ 1u, 0x480u + sd)) break;
         const uint32_t t_dst = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + C::kOperandCol0 +
                                sd * C::kDeqTmemCols;
 #pragma unroll
@@ -622,8 +643,14 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const bool whole = (step0 == 0) && (seg_end == tile_end);
         // TA: the MMA issuers take alternate units of the CTA's run; in a one-unit segment
         // only one of them has written its accumulators
-        const bool issuer_has_units[2] = {(seg_end - u >= 2) || (((u - u_begin) & 1) == 0),
-                                          (seg_end - u >= 2) || (((u - u_begin) & 1) == 1)};
+        bool issuer_has_units[C::kIssuers];
+#pragma unroll
+        for (int i = 0; i < C::kIssuers; ++i) {
+          // units of the segment are it0 .. it0 + len - 1; issuer i owns those with it % kIssuers == i
+          const long long it0 = u - u_begin, len = seg_end - u;
+          const long long first = it0 + ((i - it0 % C::kIssuers) + C::kIssuers) % C::kIssuers;
+          issuer_has_units[i] = first < it0 + len;
+        }
         const uint32_t buf = seg & 1u, pacc = (seg >> 1) & 1u;
         ++seg;
         u = seg_end;
@@ -646,7 +673,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           for (int j = 0; j < 16; ++j) v[j] = 0.f;
 #pragma unroll
           for (int acc = 0; acc < C::kAccs; ++acc) {
-            if (TA && !issuer_has_units[acc / (C::kAccs / 2)]) continue;   // stale accumulators
+            if (TA && !issuer_has_units[acc / (C::kAccs / C::kIssuers)]) continue;   // stale accumulators
             uint32_t r[16];
             tmem_ld(taddr + acc * MTMAX + cc, r);
             tmem_wait_ld(r);
@@ -777,14 +804,14 @@ Geometry geometry_of(const W4A16Args& a) {
   return g;
 }
 
-// Encodes the tensor maps and enqueues the kernel on scratch memory the caller
-// of this function has already obtained (counters first, then the slots).
-ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, uint8_t* scratch, unsigned int* fault_word,
-                          cudaStream_t stream) {
+// Encodes the tensor maps and enqueues the kernel on scratch memory the caller of this
+// function has already obtained: the per-tile arrival counters (all zero on entry; the
+// kernel leaves them zero) and the fp32 partial slots.
+ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, unsigned int* counters, float* slots,
+                          unsigned int* fault_word, cudaStream_t stream) {
   const bool bf16 = a.dtype == KS_DTYPE_BF16;
   const int mt = g.mt, mtmax = g.mtmax, n_tiles = g.n_tiles, k_steps = g.k_steps, grid = g.grid,
             max_parts = g.max_parts;
-  const size_t counter_bytes = g.counter_bytes;
   const CUtensorMapDataType dt16 = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   // Decode shapes hand the weights over in tensor memory unless told otherwise; that path
   // loads the packed weight two K-steps at a time.
@@ -827,8 +854,8 @@ ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, uint8_t* scratc
   p.bias = a.bias;
   p.scales = a.scales;
   p.zeros = a.zeros;
-  p.counters = reinterpret_cast<unsigned int*>(scratch);
-  p.slots = reinterpret_cast<float*>(scratch + counter_bytes);
+  p.counters = counters;
+  p.slots = slots;
   p.fault_word = fault_word;
   p.m = static_cast<int>(a.m);
   p.n = static_cast<int>(a.n);
@@ -858,9 +885,13 @@ ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, uint8_t* scratc
 
 ks_status_t launch_w4a16(const W4A16Args& a, cudaStream_t stream) {
   const Geometry g = geometry_of(a);
-  uint8_t* scratch = static_cast<uint8_t*>(stream_scratch(stream, g.counter_bytes + g.slot_bytes));
-  if (scratch == nullptr) KSB_FAIL(KS_ERROR_OUT_OF_MEMORY, "ks_gemm_w4a16: workspace allocation failed");
-  return enqueue_w4a16(a, g, scratch, kernel_fault_word(), stream);
+  // Counters and slots are separate allocations: the counters must be zero whenever no
+  // kernel is running, and a region that another shape used for partial sums is not.
+  float* slots = static_cast<float*>(stream_scratch(stream, g.slot_bytes, 0));
+  unsigned int* counters = static_cast<unsigned int*>(stream_scratch(stream, g.counter_bytes, 1));
+  if (slots == nullptr || counters == nullptr)
+    KSB_FAIL(KS_ERROR_OUT_OF_MEMORY, "ks_gemm_w4a16: workspace allocation failed");
+  return enqueue_w4a16(a, g, counters, slots, kernel_fault_word(), stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -925,7 +956,8 @@ ks_status_t launch_w4a16_static(const W4A16Args& a, cudaStream_t stream) {
   // an aborted one may not); the slots are fully overwritten before being read.
   cudaError_t e = cudaMemsetAsync(scratch, 0, g.counter_bytes, stream);
   if (e != cudaSuccess) return cuda_status(e, "ks_gemm_w4a16_static_scratch: cudaMemsetAsync");
-  return enqueue_w4a16(a, g, scratch, kernel_fault_word_if_ready(), stream);
+  return enqueue_w4a16(a, g, reinterpret_cast<unsigned int*>(scratch),
+                       reinterpret_cast<float*>(scratch + g.counter_bytes), kernel_fault_word_if_ready(), stream);
 }
 
 }  // namespace sm100

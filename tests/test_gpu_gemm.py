@@ -191,6 +191,8 @@ class w4_path:
     (77, 384, 512, 128, torch.float16, "fraction", False),   # non-integer zero-points: exact fp32 path
     (300, 256, 640, 128, torch.bfloat16, "eight", True),     # several token tiles
     (32, 4096, 28672 // 8, 128, torch.bfloat16, "eight", False),
+    (4, 4096, 14336, 128, torch.bfloat16, "random", False),   # ~24 units per CTA: every ring wraps several times
+    (16, 7168, 4608, 128, torch.float16, "eight", True),      # 56 K-steps per column tile, ~14 units per CTA
 ])
 def test_w4a16_tcgen05(ks, cuda, m, k, n, gs, dtype, zeros, bias):
     g = gen(m + k + n)
@@ -271,6 +273,31 @@ def test_w4a16_operand_paths(ks, cuda, operand, m, k, n, gs, dtype, zeros):
             os.environ["KS_B200_W4A16_OPERAND"] = old
     check_gemm(outs[operand], ref32, noise, f"w4a16 {operand} operand {m}x{n}x{k}")
     assert orc.rel_frobenius(outs["smem"].float(), outs["tmem"].float()) < 2e-3
+
+
+def test_w4a16_scratch_survives_shape_changes(ks, cuda):
+    """Split-K bookkeeping must not depend on what an earlier shape left in the library's
+    scratch memory: a problem with few column tiles (its partial sums land low in the
+    scratch) followed by one with many column tiles (whose arrival counters must all start
+    at zero), twice over."""
+    g = gen(4242)
+    cases = []
+    for (m, k, n) in ((8, 4096, 256), (4, 4096, 14336), (16, 2048, 384), (4, 4096, 14336)):
+        a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+        codes = torch.randint(0, 16, (k, n), generator=g).to(torch.int32)
+        scales = (torch.randn(k // 128, n, generator=g).mul(0.02).abs() + 1e-3).to(torch.bfloat16)
+        zp = torch.randint(0, 16, (k // 128, n), generator=g).to(torch.bfloat16)
+        bp = orc.pack_int4_bytes(codes)
+        cases.append((m, k, n, a, bp, scales, zp))
+    with w4_path("tcgen05"):
+        outs = [ks.dispatch.w4a16(a.to(cuda), bp.to(cuda), sc.to(cuda), zp.to(cuda), group_size=128)
+                for (_, _, _, a, bp, sc, zp) in cases]
+        torch.cuda.synchronize()
+        ks.runtime.stream_synchronize(0)
+    for (m, k, n, a, bp, sc, zp), out in zip(cases, outs):
+        ref32 = orc.w4a16(a, bp, sc, zp, 128, None, out_dtype=None)
+        noise = accumulation_noise(a.float().abs(), orc.w4a16_weight(bp, sc, zp, 128).float().abs(), k)
+        check_gemm(out.cpu(), ref32, noise, f"w4a16 in sequence {m}x{n}x{k}")
 
 
 def test_w4a16_golden(ks, cuda):
