@@ -22,7 +22,7 @@ class Bar:
         if s.pending==0: s.phase+=1; s.pending=s.count
     def done(s, parity): return (s.phase & 1) != parity
 def run_start(units, ctas, c): return (units*c)//ctas
-def sim_cta(ub, ue, k_steps, K=3, G=4, RS=8, AS=8, DS=4, verbose=False):
+def sim_cta(ub, ue, k_steps, K=2, G=4, RS=8, AS=8, DS=4, order=None):
     raw_full=[Bar(1) for _ in range(RS)]; raw_empty=[Bar(2) for _ in range(RS)]
     act_full=[Bar(1) for _ in range(AS)]; act_empty=[Bar(1) for _ in range(AS)]
     deq_full=[Bar(1) for _ in range(DS)]; deq_empty=[Bar(1) for _ in range(DS)]
@@ -32,14 +32,14 @@ def sim_cta(ub, ue, k_steps, K=3, G=4, RS=8, AS=8, DS=4, verbose=False):
         itb=0
         for b in range(b_begin,b_end):
             sr=itb%RS; pr=(itb//RS)&1
-            yield ('wait', raw_empty[sr], pr^1, 'wprod raw_empty')
+            yield ('wait', raw_empty[sr], pr^1, itb//RS, 'wprod raw_empty')
             raw_full[sr].arrive()
             itb+=1
     def aprod():
         it=0
         for u in range(ub,ue):
             sa=it%AS; pa=(it//AS)&1
-            yield ('wait', act_empty[sa], pa^1, 'aprod act_empty')
+            yield ('wait', act_empty[sa], pa^1, it//AS, 'aprod act_empty')
             act_full[sa].arrive()
             it+=1
     def issuer(i):
@@ -55,14 +55,14 @@ def sim_cta(ub, ue, k_steps, K=3, G=4, RS=8, AS=8, DS=4, verbose=False):
             buf=seg&1; pacc=(seg>>1)&1
             if seg_first: n_in_seg=0
             if mine:
-                if n_in_seg==0: yield ('wait', acc_empty[buf], pacc^1, f'issuer{i} acc_empty u={u}')
-                yield ('wait', deq_full[sd], pd, f'issuer{i} deq_full u={u}')
-                yield ('wait', act_full[sa], pa, f'issuer{i} act_full u={u}')
+                if n_in_seg==0: yield ('wait', acc_empty[buf], pacc^1, seg>>1, f'issuer{i} acc_empty u={u}')
+                yield ('wait', deq_full[sd], pd, it//DS+1, f'issuer{i} deq_full u={u}')
+                yield ('wait', act_full[sa], pa, it//AS+1, f'issuer{i} act_full u={u}')
                 n_in_seg+=1
                 deq_empty[sd].arrive(); act_empty[sa].arrive()
                 if my_last: acc_full[buf].arrive()
             elif seg_last and n_in_seg==0:
-                yield ('wait', acc_empty[buf], pacc^1, f'issuer{i} idle acc_empty u={u}')
+                yield ('wait', acc_empty[buf], pacc^1, seg>>1, f'issuer{i} idle acc_empty u={u}')
                 acc_full[buf].arrive()
             if seg_last: seg+=1
             it+=1; step=0 if step+1==k_steps else step+1
@@ -76,8 +76,8 @@ def sim_cta(ub, ue, k_steps, K=3, G=4, RS=8, AS=8, DS=4, verbose=False):
             if u<ub or u>=ue:
                 raw_empty[sr].arrive(); b+=stride; continue
             it=u-ub; sd=it%DS; pd=(it//DS)&1
-            yield ('wait', raw_full[sr], pr, f'group{g} raw_full u={u}')
-            yield ('wait', deq_empty[sd], pd^1, f'group{g} deq_empty u={u}')
+            yield ('wait', raw_full[sr], pr, itb//RS+1, f'group{g} raw_full u={u}')
+            yield ('wait', deq_empty[sd], pd^1, it//DS, f'group{g} deq_empty u={u}')
             raw_empty[sr].arrive()
             deq_full[sd].arrive()
             b+=stride
@@ -89,43 +89,55 @@ def sim_cta(ub, ue, k_steps, K=3, G=4, RS=8, AS=8, DS=4, verbose=False):
             seg_end=min(tile_end,ue)
             buf=seg&1; pacc=(seg>>1)&1
             seg+=1; u=seg_end
-            yield ('wait', acc_full[buf], pacc, f'epilogue acc_full seg={seg-1}')
+            yield ('wait', acc_full[buf], pacc, ((seg-1)>>1)+1, f'epilogue acc_full seg={seg-1}')
             acc_empty[buf].arrive()
     procs={'wprod':wprod(),'aprod':aprod(),'epi':epilogue()}
     for i in range(K): procs[f'iss{i}']=issuer(i)
     for g in range(G): procs[f'grp{g}']=group(g)
     blocked={}
-    alive=set(procs)
+    alive=list(procs)
+    if order is not None:
+        order.shuffle(alive)
+    problems={}
     while alive:
         progressed=False
         for name in list(alive):
             gen=procs[name]
             while True:
                 if name in blocked:
-                    bar,par,desc=blocked[name]
+                    bar,par,want,desc=blocked[name]
                     if not bar.done(par): break
+                    if bar.phase!=want: problems[name]=f'{desc}: passed at completion {bar.phase}, meant {want}'
                     del blocked[name]; progressed=True
                 try:
                     op=next(gen)
                 except StopIteration:
-                    alive.discard(name); progressed=True; break
-                _,bar,par,desc=op
-                if bar.done(par): progressed=True; continue
-                blocked[name]=(bar,par,desc); break
+                    alive.remove(name); progressed=True; break
+                _,bar,par,want,desc=op
+                if bar.done(par):
+                    if bar.phase!=want: problems[name]=f'{desc}: passed at completion {bar.phase}, meant {want}'
+                    progressed=True; continue
+                blocked[name]=(bar,par,want,desc); break
         if not progressed:
-            return {n:blocked[n][2] for n in blocked}
-    return None
+            problems.update({n:'stuck at '+blocked[n][3] for n in blocked})
+            return problems
+    return problems or None
 
 
 def deadlocked_ctas(n_tiles, k_steps, ctas=148, **kw):
+    """CTAs whose roles get stuck or pass a wait at the wrong phase, under the natural role
+    order and under a few shuffled ones (the protocol must not depend on who runs first)."""
+    import random
     units = n_tiles * k_steps
     ctas = min(ctas, units)
     stuck = []
     for c in range(ctas):
         ub, ue = run_start(units, ctas, c), run_start(units, ctas, c + 1)
-        r = sim_cta(ub, ue, k_steps, **kw)
-        if r:
-            stuck.append((c, ub, ue, r))
+        for order in (None, random.Random(1), random.Random(2), random.Random(3)):
+            r = sim_cta(ub, ue, k_steps, order=order, **kw)
+            if r:
+                stuck.append((c, ub, ue, r))
+                break
     return stuck
 
 
