@@ -2,7 +2,8 @@
 on-device checker: ``oracle/_ref/libkernel_set_ref.so``. TEST INFRASTRUCTURE.
 
 The sources are compiled where they lie in a checkout of the reference project
-(``KS_REFERENCE_ROOT`` or ``/root/reference``); nothing is copied. The result
+(environment variable ``KS_REFERENCE_ROOT``, with the build container's checkout as the
+default); nothing is copied. The result
 is git-ignored. When the checkout is absent (a machine that only received the
 prebuilt file) the function reports that and returns ``None``.
 

@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz by running the REFERENCE project's own Python
 code on the CPU. Run once in a container that holds a checkout of the
-reference (``KS_REFERENCE_ROOT`` or ``/root/reference``); the tests only read
+reference (environment variable ``KS_REFERENCE_ROOT``); the tests only read
 the frozen vectors.
 
 How the reference is made to run without a GPU:
