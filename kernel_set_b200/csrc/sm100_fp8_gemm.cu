@@ -55,6 +55,9 @@ namespace {
 #ifndef KSB_FP8_ACC_BUFS_128
 #define KSB_FP8_ACC_BUFS_128 4
 #endif
+#ifndef KSB_FP8_PANEL
+#define KSB_FP8_PANEL 4
+#endif
 #ifndef KSB_FP8_SCALE_GROUP
 #define KSB_FP8_SCALE_GROUP 2
 #endif
@@ -129,11 +132,20 @@ __device__ __forceinline__ bool locate_tile(const Params& p, const int* prefix, 
                                             TileCoord* tc) {
   if constexpr (!GROUPED) {
     if (t >= p.tiles_m * p.tiles_n) return false;
-    const int mt = t / p.tiles_n;
+    // Column panels of kPanel tiles, all row tiles of a panel before the next panel: the
+    // tiles in flight at any time then share a few B panels and sweep A, so the set that has
+    // to stay in L2 between rounds is A (small) instead of all of B.
+    constexpr int kPanel = KSB_FP8_PANEL;
+    const int per_panel = kPanel * p.tiles_m;
+    const int panel = t / per_panel;
+    const int r = t - panel * per_panel;
+    const int width = (p.tiles_n - panel * kPanel) < kPanel ? (p.tiles_n - panel * kPanel) : kPanel;
+    const int mt = r / width;
+    const int nt = panel * kPanel + (r - mt * width);
     tc->expert = 0;
     tc->row0 = mt * kBM;
     tc->row_end = p.m;
-    tc->n0 = (t - mt * p.tiles_n) * BN;
+    tc->n0 = nt * BN;
     return true;
   } else {
     const int total_mt = prefix[p.num_experts];
