@@ -540,7 +540,7 @@ def main():
                          "frac": achieved / fp8_peak,
                          # dram__bytes_read.sum + dram__bytes_write.sum of this kernel on this workload from
                          # one ncu capture (profiles/fp8_blockwise_umma_kernel_cfg2.md); algorithmic bytes 140.4e6
-                         "traffic": 222.7e6 if (world == 1 and m == M) else None,
+                         "traffic": 133.4e6 if (world == 1 and m == M) else None,
                          "kernel": "fp8_blockwise_umma_kernel", "us_per_launch": gemm_ms * 1e3,
                          "peak_source": f"2 x {peaks['source']} sustained cuBLAS bf16 ({peaks['bf16_sustained']} TFLOP/s); "
                                         "no FP8 figure was measured on this pool",
