@@ -534,10 +534,14 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
   const int experts = grouped ? a.num_experts : 1;
   const int sms = sm_count();
   const int64_t tiles_m_bound = grouped ? (a.m + kBM - 1) / kBM + experts : (a.m + kBM - 1) / kBM;
-  // Wide tiles halve the shared-memory traffic per flop; use them once they
-  // still give every SM a tile.
+  // Tile width by estimated time: rounds of tiles over the SMs times the measured cost of a
+  // K-block of that width (~850 cycles for 128 x 256, ~550 for 128 x 128). Wide tiles win
+  // as soon as they do not need more rounds than narrow ones would save.
   const int64_t tiles256 = tiles_m_bound * ((a.n + 255) / 256);
-  const int bn = (a.force_bn == 128 || a.force_bn == 256) ? a.force_bn : (tiles256 >= sms ? 256 : 128);
+  const int64_t tiles128 = tiles_m_bound * ((a.n + 127) / 128);
+  const int64_t cost256 = ((tiles256 + sms - 1) / sms) * 850;
+  const int64_t cost128 = ((tiles128 + sms - 1) / sms) * 550;
+  const int bn = (a.force_bn == 128 || a.force_bn == 256) ? a.force_bn : (cost256 <= cost128 ? 256 : 128);
 
   CUtensorMap tm_a, tm_b;
   {
