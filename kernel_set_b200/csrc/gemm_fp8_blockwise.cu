@@ -13,18 +13,26 @@ namespace ksb {
 namespace {
 
 // KS_B200_FP8_PATH=general pins the general kernel, =tcgen05 refuses to fall
-// back (UNSUPPORTED_SHAPE instead); KS_B200_FP8_BN=128|256 pins the tile width.
-// Both exist for tests and profiling; unset means "choose".
-int env_path() {
-  const char* v = std::getenv("KS_B200_FP8_PATH");
-  if (v == nullptr) return 0;
-  if (v[0] == 'g') return 1;
-  if (v[0] == 't') return 2;
-  return 0;
+// back (UNSUPPORTED_SHAPE instead); KS_B200_FP8_BN=128|256 pins the tile width;
+// KS_B200_FP8_SPLIT=0 switches the K-split of the last partial round off.
+// They exist for tests and profiling; unset means "choose". Read once per process
+// unless KS_B200_ENV_RELOAD is set (the test-suite flips them between calls).
+struct EnvChoice {
+  int path = 0;   // 0 choose, 1 general, 2 tcgen05
+  int bn = 0;
+  int split = -1; // -1 choose, 0 off, 1 on
+};
+EnvChoice read_env() {
+  EnvChoice c;
+  if (const char* v = std::getenv("KS_B200_FP8_PATH")) c.path = v[0] == 'g' ? 1 : (v[0] == 't' ? 2 : 0);
+  if (const char* v = std::getenv("KS_B200_FP8_BN")) c.bn = std::atoi(v);
+  if (const char* v = std::getenv("KS_B200_FP8_SPLIT")) c.split = std::atoi(v) != 0 ? 1 : 0;
+  return c;
 }
-int env_bn() {
-  const char* v = std::getenv("KS_B200_FP8_BN");
-  return v ? std::atoi(v) : 0;
+EnvChoice env_choice() {
+  static const bool reload = std::getenv("KS_B200_ENV_RELOAD") != nullptr;
+  static const EnvChoice cached = read_env();
+  return reload ? read_env() : cached;
 }
 
 template <typename F8, typename OutT, bool NT, bool GROUPED>
@@ -62,12 +70,11 @@ ks_status_t run(sm100::Fp8GemmArgs& a, ks_stream_t stream) {
   st = poll_kernel_fault(a.where);
   if (st != KS_SUCCESS) return st;
   cudaStream_t s = as_stream(stream);
-  const int path = env_path();
-  a.force_bn = env_bn();
-  if (path != 1 && sm100::fp8_blockwise_eligible(a)) {
-    if (a.force_bn == 0 && sm100::fp8_blockwise_pair_eligible(a)) return sm100::launch_fp8_blockwise_pair(a, s);
-    return sm100::launch_fp8_blockwise(a, s);
-  }
+  const EnvChoice env = env_choice();
+  const int path = env.path;
+  a.force_bn = env.bn;
+  a.force_split = env.split;
+  if (path != 1 && sm100::fp8_blockwise_eligible(a)) return sm100::launch_fp8_blockwise(a, s);
   if (path == 2)
     KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE, std::string(a.where) + ": shape not eligible for the tcgen05 kernel");
   const int64_t tiles_m = (a.m + general::kTM - 1) / general::kTM + a.num_experts;

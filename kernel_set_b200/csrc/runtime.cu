@@ -9,6 +9,7 @@
 
 #include "common.cuh"
 #include "kernel_set/runtime.h"
+#include "sm100_host.cuh"
 
 namespace ksb {
 
@@ -103,6 +104,9 @@ ks_status_t poll_kernel_fault(const char* where) {
   const unsigned int code = *static_cast<volatile unsigned int*>(d->fault_host);
   if (code == 0u) return KS_SUCCESS;
   *static_cast<volatile unsigned int*>(d->fault_host) = 0u;
+  // a kernel that stopped half-way may have left split-K arrival counters non-zero
+  sm100::stream_scratch_mark_dirty(1);
+  sm100::stream_scratch_mark_dirty(3);
   char buf[160];
   snprintf(buf, sizeof(buf),
            "%s: an earlier kernel on this device gave up on a bounded wait (code 0x%08x)",
@@ -188,6 +192,8 @@ ks_status_t ks_stream_create(ks_stream_t* out_stream) {
 }
 
 ks_status_t ks_stream_destroy(ks_stream_t stream) {
+  // library-owned workspace of this stream goes with it (a later stream may reuse the handle value)
+  ksb::sm100::stream_scratch_release(as_stream(stream));
   return cuda_status(cudaStreamDestroy(as_stream(stream)), "ks_stream_destroy");
 }
 

@@ -24,6 +24,13 @@
 //               the last K-block rounds once to the output type. Dense problems
 //               stage the tile in swizzled shared memory and leave by TMA store;
 //               grouped and unaligned ones store row segments from registers.
+// Last partial round of a dense problem: when T tiles leave T mod #CTAs tiles for a final
+// round that would keep most SMs idle (896 tiles on 148 SMs: 8 tiles, 140 idle SMs for a
+// whole tile time), those tiles are cut along K into S parts (S <= 8, parts x tiles <=
+// #CTAs). Each part's epilogue warps write their fp32 partial to a slot; per (tile, warp,
+// 32-column slice) a counter finds the last part to arrive, which adds the parts in part
+// order (reproducible) and stores the slice. Parts bump their slices' counters in rotated
+// order, so parts that finish together each end up reducing a different slice; nobody waits.
 // Measured on B200 (in-kernel cycle counters): a K-block of a 128 x 256 tile takes
 // ~850 cycles against 512 of tensor work. The epilogue's share is a serial chain per
 // warp (barrier test ~100, eight dependent TMEM loads ~55 each, 128 FMAs per thread:
@@ -121,16 +128,37 @@ struct Params {
   uint32_t idesc;
   int vec_store;  // 16-byte output stores are legal
   int tma_store;  // dense problems: finished tiles leave through shared memory and TMA stores
+  // K-split of the last partial round (dense only): work items [0, split_from) are whole
+  // tiles; item split_from + r is part r % split_s of tile split_from + r / split_s.
+  int split_from;
+  int split_s;            // 1 = no split
+  float4* split_slots;    // [tail tile][part][epilogue warp][16-byte column chunk][lane]
+  unsigned int* split_counters;  // [tail tile][epilogue warp][32-column slice], zero between launches
 };
 
 struct TileCoord {
   int expert, row0, row_end, n0;
+  int kb0, kb1;   // K-blocks of this work item
+  int part;       // -1: whole tile; else index of this K-part
+  int tail;       // index of the tile among the split tiles
 };
 
 template <int BN, bool GROUPED>
 __device__ __forceinline__ bool locate_tile(const Params& p, const int* prefix, const int* offs, int t,
                                             TileCoord* tc) {
   if constexpr (!GROUPED) {
+    tc->kb0 = 0;
+    tc->kb1 = p.nkb;
+    tc->part = -1;
+    tc->tail = 0;
+    if (t >= p.split_from) {
+      const int r = t - p.split_from;
+      tc->tail = r / p.split_s;
+      tc->part = r - tc->tail * p.split_s;
+      tc->kb0 = (tc->part * p.nkb) / p.split_s;
+      tc->kb1 = ((tc->part + 1) * p.nkb) / p.split_s;
+      t = p.split_from + tc->tail;
+    }
     if (t >= p.tiles_m * p.tiles_n) return false;
     // Column panels of kPanel tiles, all row tiles of a panel before the next panel: the
     // tiles in flight at any time then share a few B panels and sweep A, so the set that has
@@ -148,6 +176,10 @@ __device__ __forceinline__ bool locate_tile(const Params& p, const int* prefix, 
     tc->n0 = nt * BN;
     return true;
   } else {
+    tc->kb0 = 0;
+    tc->kb1 = p.nkb;
+    tc->part = -1;
+    tc->tail = 0;
     const int total_mt = prefix[p.num_experts];
     if (t >= total_mt * p.tiles_n) return false;
     const int mt = t / p.tiles_n;
@@ -240,7 +272,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     bool ok = true;
     TileCoord tc;
     for (int t = blockIdx.x; ok && locate_tile<BN, GROUPED>(p, prefix, offs, t, &tc); t += gridDim.x) {
-      for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+      for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
         const uint32_t s = it % C::kStages;
         const uint32_t ph = (it / C::kStages) & 1u;
         if (!mbar_wait(wctx, bar_empty + 8 * s, ph ^ 1u, 0x100u + s)) { ok = false; break; }
@@ -267,7 +299,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     bool ok = true;
     TileCoord tc;
     for (int t = blockIdx.x; ok && locate_tile<BN, GROUPED>(p, prefix, offs, t, &tc); t += gridDim.x) {
-      for (int kb = 0; kb < p.nkb; ++kb, ++it) {
+      for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
         const uint32_t s = it % C::kStages;
         const uint32_t ph = (it / C::kStages) & 1u;
         const uint32_t buf = it % C::kAccBufs;
@@ -331,21 +363,21 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
 #pragma unroll
         for (int j = 0; j < G; ++j) {
           const int kb = kb0 + j;
-          const bool in = kb < p.nkb;
+          const bool in = kb < tc.kb1;
           as_nxt[j] = (in && row_ok) ? __ldg(as_ptr + kb) : 0.f;
           bs_nxt[j] = in ? __ldg(bs_ptr + static_cast<size_t>(kb) * bs_step) : 0.f;
         }
       };
-      fetch_scales(0);
+      fetch_scales(tc.kb0);
 
-      for (int kb0 = 0; kb0 < p.nkb && ok; kb0 += G) {
+      for (int kb0 = tc.kb0; kb0 < tc.kb1 && ok; kb0 += G) {
         float sc[G];
 #pragma unroll
         for (int j = 0; j < G; ++j) sc[j] = as_nxt[j] * bs_nxt[j];
         fetch_scales(kb0 + G);
 #pragma unroll
         for (int j4 = 0; j4 < G; ++j4) {
-          if (kb0 + j4 >= p.nkb) break;
+          if (kb0 + j4 >= tc.kb1) break;
           const float2 scale2 = make_float2(sc[j4], sc[j4]);
           const uint32_t buf = it % C::kAccBufs;
           const uint32_t aph = (it / C::kAccBufs) & 1u;
@@ -388,7 +420,62 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
       }
       bool stored = false;
       if constexpr (!GROUPED) {
-        if (ok && p.tma_store) {
+        if (ok && tc.part >= 0) {
+          // One K-part of a split tile. The warp's 32 x EC partial goes to its slot (a lane
+          // writes and later reads the same addresses, 16 bytes per column chunk, chunks 512 B
+          // apart: every store and load of the warp is one contiguous 512-byte piece).
+          constexpr int kChunks = EC / 4;      // float4 chunks per lane
+          constexpr int kSlices = EC / 32;     // 32-column slices, one counter each
+          const int ew = warp - 4;
+          const size_t warp_f4 = static_cast<size_t>(kChunks) * 32;
+          float4* mine = p.split_slots + ((static_cast<size_t>(tc.tail) * p.split_s + tc.part) * C::kEpiWarps + ew) * warp_f4 + lane;
+#pragma unroll
+          for (int c4 = 0; c4 < kChunks; ++c4)
+            __stcg(mine + c4 * 32, make_float4(acc[2 * c4].x, acc[2 * c4].y, acc[2 * c4 + 1].x, acc[2 * c4 + 1].y));
+          __threadfence();
+          __syncwarp();
+          unsigned int* ctr = p.split_counters + (static_cast<size_t>(tc.tail) * C::kEpiWarps + ew) * kSlices;
+#pragma unroll 1
+          for (int j = 0; j < kSlices; ++j) {
+            const int sl = (tc.part + j) % kSlices;
+            unsigned int prev = 0u;
+            if (lane == 0) prev = atomicAdd(ctr + sl, 1u);
+            prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
+            if (prev != static_cast<unsigned int>(p.split_s - 1)) continue;
+            // this warp completes the slice: parts are added in part order
+            if (lane == 0) ctr[sl] = 0u;   // ready for the next launch
+            __threadfence();
+            float4 sum[8];
+#pragma unroll
+            for (int c4 = 0; c4 < 8; ++c4) sum[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int q = 0; q < p.split_s; ++q) {
+              const float4* src = p.split_slots + ((static_cast<size_t>(tc.tail) * p.split_s + q) * C::kEpiWarps + ew) * warp_f4 + lane + sl * 8 * 32;
+              float4 v[8];
+#pragma unroll
+              for (int c4 = 0; c4 < 8; ++c4) v[c4] = __ldcg(src + c4 * 32);
+#pragma unroll
+              for (int c4 = 0; c4 < 8; ++c4) {
+                sum[c4].x += v[c4].x; sum[c4].y += v[c4].y; sum[c4].z += v[c4].z; sum[c4].w += v[c4].w;
+              }
+            }
+            if (row_ok) {
+              OutT* dst = out + static_cast<size_t>(row) * p.n + col0 + sl * 32;
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int valid = p.n - (col0 + sl * 32 + h * 16);
+                float v16[16];
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                  v16[4 * c4] = sum[4 * h + c4].x; v16[4 * c4 + 1] = sum[4 * h + c4].y;
+                  v16[4 * c4 + 2] = sum[4 * h + c4].z; v16[4 * c4 + 3] = sum[4 * h + c4].w;
+                }
+                if (valid > 0) store_16<OutT>(dst + h * 16, v16, p.vec_store != 0, valid);
+              }
+            }
+          }
+          stored = true;
+        }
+        if (ok && !stored && p.tma_store) {
           // The warp's 32 x EC block leaves in pieces of 32 rows x 128 bytes: written
           // to shared memory in the 128-byte swizzle (conflict-free: lanes 0-7 hit eight
           // different 16-byte columns), then one TMA store, which clips rows and columns
@@ -586,6 +673,39 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
 
   int64_t tiles = tiles_m_bound * p.tiles_n;
   const int grid = static_cast<int>(tiles < sms ? (tiles < 1 ? 1 : tiles) : sms);
+
+  // K-split of the last partial round (dense problems only). Worth it when the tiles left
+  // over after the full rounds occupy at most half of the CTAs and every part keeps at least
+  // four K-blocks; the part count is capped at eight (each part costs the finishing warp one
+  // more partial to read).
+  p.split_from = static_cast<int>(tiles);
+  p.split_s = 1;
+  p.split_slots = nullptr;
+  p.split_counters = nullptr;
+  if (!grouped && a.force_split != 0 && tiles > grid) {
+    const int rem = static_cast<int>(tiles % grid);
+    int s = rem > 0 ? grid / rem : 1;
+    if (s > 8) s = 8;
+    while (s > 1 && p.nkb / s < 4) --s;
+    if (rem > 0 && s >= 2) {
+      const int epi_warps = bn == 256 ? Cfg<256>::kEpiWarps : Cfg<128>::kEpiWarps;
+      const int epi_cols = bn == 256 ? Cfg<256>::kEpiCols : Cfg<128>::kEpiCols;
+      const size_t slot_bytes = static_cast<size_t>(rem) * s * kBM * bn * sizeof(float);
+      const size_t counter_bytes = static_cast<size_t>(rem) * epi_warps * (epi_cols / 32) * sizeof(unsigned int);
+      float4* slots = static_cast<float4*>(stream_scratch(stream, slot_bytes, 2));
+      unsigned int* counters = static_cast<unsigned int*>(stream_scratch(stream, counter_bytes, 3));
+      if (slots != nullptr && counters != nullptr) {
+        if (stream_scratch_take_dirty(stream, 3)) {
+          cudaError_t e = cudaMemsetAsync(counters, 0, stream_scratch_bytes(stream, 3), stream);
+          if (e != cudaSuccess) return cuda_status(e, a.where);
+        }
+        p.split_from = static_cast<int>(tiles) - rem;
+        p.split_s = s;
+        p.split_slots = slots;
+        p.split_counters = counters;
+      }
+    }
+  }
   return bn == 256 ? launch_bn<256>(a, tm_a, tm_b, p, grid, stream) : launch_bn<128>(a, tm_a, tm_b, p, grid, stream);
 }
 

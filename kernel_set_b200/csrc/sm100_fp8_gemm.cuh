@@ -24,6 +24,7 @@ struct Fp8GemmArgs {
   bool e5m2 = false;
   ks_dtype_t out_dtype = KS_DTYPE_BF16;
   int force_bn = 0;                // 128 / 256 pins the tile width (tests), 0 = choose
+  int force_split = -1;            // K-split of the last partial round: -1 choose, 0 never, 1 whenever legal
 };
 
 // True when the tcgen05 kernel can take the problem (128 x 128 scale blocks,
@@ -32,11 +33,6 @@ bool fp8_blockwise_eligible(const Fp8GemmArgs& a);
 
 // Encodes the tensor maps and enqueues one persistent launch on `stream`.
 ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream);
-
-// CTA-pair (cta_group::2) kernel for dense problems: 256 x 256 tiles per pair of
-// SMs. `eligible` also consults KS_B200_FP8_PAIR (0 = never, 1 = whenever legal).
-bool fp8_blockwise_pair_eligible(const Fp8GemmArgs& a);
-ks_status_t launch_fp8_blockwise_pair(const Fp8GemmArgs& a, cudaStream_t stream);
 
 }  // namespace sm100
 }  // namespace ksb

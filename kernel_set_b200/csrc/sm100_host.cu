@@ -29,6 +29,7 @@ EncodeTiledFn encode_fn() {
 struct Scratch {
   void* ptr = nullptr;
   size_t bytes = 0;
+  bool dirty = false;
 };
 std::mutex g_scratch_mutex;
 std::map<std::pair<std::pair<int, cudaStream_t>, int>, Scratch> g_scratch;
@@ -78,6 +79,47 @@ void* stream_scratch(cudaStream_t stream, size_t bytes, int kind) {
   s.ptr = fresh;
   s.bytes = want;
   return fresh;
+}
+
+size_t stream_scratch_bytes(cudaStream_t stream, int kind) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  auto it = g_scratch.find(std::make_pair(std::make_pair(dev, stream), kind));
+  return it == g_scratch.end() ? 0 : it->second.bytes;
+}
+
+void stream_scratch_mark_dirty(int kind) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  for (auto& kv : g_scratch)
+    if (kv.first.first.first == dev && kv.first.second == kind) kv.second.dirty = true;
+}
+
+bool stream_scratch_take_dirty(cudaStream_t stream, int kind) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  auto it = g_scratch.find(std::make_pair(std::make_pair(dev, stream), kind));
+  if (it == g_scratch.end() || !it->second.dirty) return false;
+  it->second.dirty = false;
+  return true;
+}
+
+void stream_scratch_release(cudaStream_t stream) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  for (auto it = g_scratch.begin(); it != g_scratch.end();) {
+    if (it->first.first.first == dev && it->first.first.second == stream) {
+      if (it->second.ptr != nullptr) cudaFreeAsync(it->second.ptr, stream);
+      it = g_scratch.erase(it);
+    } else {
+      ++it;
+    }
+  }
+  cudaGetLastError();
 }
 
 }  // namespace sm100

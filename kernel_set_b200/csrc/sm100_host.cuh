@@ -27,6 +27,16 @@ bool tma_encode(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const voi
 // (cudaMallocAsync / cudaFreeAsync), so work already queued on the stream keeps its buffer.
 // Returns NULL when the allocation fails.
 void* stream_scratch(cudaStream_t stream, size_t bytes, int kind = 0);
+// Size of that buffer (0 when none exists).
+size_t stream_scratch_bytes(cudaStream_t stream, int kind);
+// Marks every buffer of `kind` on the current device as possibly modified by a kernel
+// that stopped half-way; stream_scratch_take_dirty() reports and clears the mark of one
+// (device, stream) buffer, whose owner then restores the buffer's invariant.
+void stream_scratch_mark_dirty(int kind);
+bool stream_scratch_take_dirty(cudaStream_t stream, int kind);
+// Frees (stream-ordered) every buffer of the current device that belongs to `stream`;
+// called when the stream is destroyed, so that a recycled handle starts clean.
+void stream_scratch_release(cudaStream_t stream);
 
 }  // namespace sm100
 }  // namespace ksb

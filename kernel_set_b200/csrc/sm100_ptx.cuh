@@ -457,77 +457,5 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-// ---- thread-block clusters and CTA pairs (cta_group::2) -------------------------------
-__device__ __forceinline__ uint32_t cluster_cta_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// Cluster-wide barrier. No time limit exists for it: only call it where every
-// thread of both CTAs is certain to arrive (all other waits are bounded).
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// shared::cluster address of `smem_addr` (a shared::cta address) in CTA `rank`.
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-// Arrive on a barrier that may live in the other CTA of the cluster.
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result_addr, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result_addr),
-               "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-// One MMA across the CTA pair: M = 256 (128 rows from each CTA's A tile), B's N
-// rows split between the two CTAs' shared memory, D in both CTAs' TMEM.
-__device__ __forceinline__ void umma2_f8f6f4_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                   uint32_t accumulate) {
-  asm volatile("{\n\t.reg .pred p;\n\t" KSB_ELECT_PROLOGUE
-               "setp.ne.b32 p, %4, 0;\n\t"
-               "@q tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
-               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-               : "memory");
-}
-// Commit of the pair's MMAs: arrives on the barrier at the same shared-memory
-// offset in every CTA named by `cta_mask` (an arrival signal, not a data copy).
-__device__ __forceinline__ void tc_commit_pair_elect(uint32_t bar, uint16_t cta_mask) {
-  asm volatile("{\n\t" KSB_ELECT_PROLOGUE
-               "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               "\n\t}\n" ::"r"(bar),
-               "h"(cta_mask)
-               : "memory");
-}
-// TMA tile loads issued by a CTA of a pair: data lands in the issuing CTA's own
-// shared memory, completion bytes are counted on `bar_cluster_addr`, which may
-// be the other CTA's barrier.
-__device__ __forceinline__ void tma_load_2d_pair_elect(uint32_t smem_dst, const CUtensorMap* m,
-                                                       uint32_t bar_cluster_addr, int x, int y) {
-  asm volatile("{\n\t" KSB_ELECT_PROLOGUE
-               "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], "
-               "[%1, {%3, %4}], [%2];\n\t}\n" ::"r"(smem_dst),
-               "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void tma_load_3d_pair_elect(uint32_t smem_dst, const CUtensorMap* m,
-                                                       uint32_t bar_cluster_addr, int x, int y, int z) {
-  asm volatile("{\n\t" KSB_ELECT_PROLOGUE
-               "@q cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], "
-               "[%1, {%3, %4, %5}], [%2];\n\t}\n" ::"r"(smem_dst),
-               "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
-               : "memory");
-}
-
 }  // namespace sm100
 }  // namespace ksb

@@ -153,17 +153,6 @@ struct Params {
   uint32_t idesc;
 };
 
-// Units (tile * k_steps + step) are dealt in equal contiguous runs.
-__device__ __forceinline__ long long run_start(long long units, int ctas, int c) {
-  return (units * c) / ctas;
-}
-__device__ __forceinline__ int cta_of_unit(long long units, int ctas, long long u) {
-  int c = static_cast<int>((u * ctas) / units);
-  while (c + 1 < ctas && run_start(units, ctas, c + 1) <= u) ++c;
-  while (c > 0 && run_start(units, ctas, c) > u) --c;
-  return c;
-}
-
 template <typename T> struct Pack16;
 template <> struct Pack16<__nv_bfloat16> {
   using V2 = __nv_bfloat162;
@@ -783,8 +772,8 @@ bool w4a16_eligible(const W4A16Args& a) {
 namespace {
 
 struct Geometry {
-  int mt, mtmax, n_tiles, k_steps, grid, max_parts;
-  size_t counter_bytes, slot_bytes;
+  int mt = 0, mtmax = 0, n_tiles = 0, k_steps = 0, grid = 0, max_parts = 0;
+  size_t counter_bytes = 0, slot_bytes = 0;
 };
 
 Geometry geometry_of(const W4A16Args& a) {
@@ -883,14 +872,30 @@ ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, unsigned int* c
 
 }  // namespace
 
+// The register-operand decode kernel takes every problem it can, unless the caller pinned
+// the tcgen05 kernel.
+bool use_decode_kernel(const W4A16Args& a) { return a.kernel != 1 && decode::eligible(a); }
+
 ks_status_t launch_w4a16(const W4A16Args& a, cudaStream_t stream) {
-  const Geometry g = geometry_of(a);
   // Counters and slots are separate allocations: the counters must be zero whenever no
   // kernel is running, and a region that another shape used for partial sums is not.
-  float* slots = static_cast<float*>(stream_scratch(stream, g.slot_bytes, 0));
-  unsigned int* counters = static_cast<unsigned int*>(stream_scratch(stream, g.counter_bytes, 1));
+  // The tcgen05 kernel can give up on a bounded wait and leave counters non-zero; when
+  // the fault poll has reported such a launch on this device, every stream's counters are
+  // cleared before their next use (stream_scratch_dirty).
+  const bool dec = use_decode_kernel(a);
+  const Geometry g = dec ? Geometry{} : geometry_of(a);
+  const decode::Geometry gd = dec ? decode::geometry_of(a) : decode::Geometry{};
+  const size_t slot_bytes = dec ? gd.slot_bytes : g.slot_bytes;
+  const size_t counter_bytes = dec ? gd.counter_bytes : g.counter_bytes;
+  float* slots = static_cast<float*>(stream_scratch(stream, slot_bytes, 0));
+  unsigned int* counters = static_cast<unsigned int*>(stream_scratch(stream, counter_bytes, 1));
   if (slots == nullptr || counters == nullptr)
     KSB_FAIL(KS_ERROR_OUT_OF_MEMORY, "ks_gemm_w4a16: workspace allocation failed");
+  if (stream_scratch_take_dirty(stream, 1)) {
+    cudaError_t e = cudaMemsetAsync(counters, 0, stream_scratch_bytes(stream, 1), stream);
+    if (e != cudaSuccess) return cuda_status(e, "ks_gemm_w4a16: clearing the split-K counters");
+  }
+  if (dec) return decode::enqueue(a, gd, counters, slots, stream);
   return enqueue_w4a16(a, g, counters, slots, kernel_fault_word(), stream);
 }
 
@@ -938,8 +943,14 @@ ks_status_t static_scratch_address(uint8_t** out) {
 size_t w4a16_static_scratch_capacity() { return kStaticScratchBytes; }
 
 ks_status_t launch_w4a16_static(const W4A16Args& a, cudaStream_t stream) {
-  const Geometry g = geometry_of(a);
-  const size_t need = g.counter_bytes + g.slot_bytes;
+  const bool dec = use_decode_kernel(a);
+  const Geometry g = dec ? Geometry{} : geometry_of(a);
+  const decode::Geometry gd = dec ? decode::geometry_of(a) : decode::Geometry{};
+  const size_t counter_bytes = dec ? gd.counter_bytes : g.counter_bytes;
+  // With several token tiles the tcgen05 kernel snaps its runs to whole column tiles and
+  // never touches the partial slots.
+  const size_t slot_bytes = dec ? gd.slot_bytes : (a.m > 128 ? 0 : g.slot_bytes);
+  const size_t need = counter_bytes + slot_bytes;
   if (need > kStaticScratchBytes) {
     char msg[224];
     snprintf(msg, sizeof(msg),
@@ -951,13 +962,20 @@ ks_status_t launch_w4a16_static(const W4A16Args& a, cudaStream_t stream) {
   uint8_t* scratch = nullptr;
   ks_status_t st = static_scratch_address(&scratch);
   if (st != KS_SUCCESS) return st;
-  // The array keeps whatever the previous call left. The kernel requires the
-  // per-tile arrival counters to be zero on entry (a clean run leaves them so,
-  // an aborted one may not); the slots are fully overwritten before being read.
-  cudaError_t e = cudaMemsetAsync(scratch, 0, g.counter_bytes, stream);
+  // The array keeps whatever the previous call left. The kernels require the
+  // arrival counters to be zero on entry (a clean run leaves them so, an aborted
+  // one may not, and another shape lays them out differently); the slots are
+  // fully overwritten before being read.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, counter_bytes, stream);
   if (e != cudaSuccess) return cuda_status(e, "ks_gemm_w4a16_static_scratch: cudaMemsetAsync");
-  return enqueue_w4a16(a, g, reinterpret_cast<unsigned int*>(scratch),
-                       reinterpret_cast<float*>(scratch + g.counter_bytes), kernel_fault_word_if_ready(), stream);
+  unsigned int* counters = reinterpret_cast<unsigned int*>(scratch);
+  float* slots = reinterpret_cast<float*>(scratch + counter_bytes);
+  if (dec) return decode::enqueue(a, gd, counters, slots, stream);
+  // The word through which a tcgen05 kernel reports a bounded wait that ran out is a pinned
+  // host allocation made by the first allocating entry point on the device; a process that
+  // only ever calls this entry point runs the tcgen05 kernel without it (the decode kernel,
+  // which serves up to 64 rows, has no such wait).
+  return enqueue_w4a16(a, g, counters, slots, kernel_fault_word_if_ready(), stream);
 }
 
 }  // namespace sm100

@@ -83,3 +83,35 @@ def accumulation_noise(a_abs: torch.Tensor, b_abs: torch.Tensor, k: int) -> torc
     4 standard deviations)."""
     eps = 2.0 ** -24
     return (a_abs.double() @ b_abs.double()).float() * (4.0 * eps * (k ** 0.5))
+
+
+def block_quant_nk_device(w_nk: torch.Tensor):
+    """128 x 128 block quantization of a [N,K] fp32 weight on its own device: the
+    reference's input preparation (benchmarks/bench.py:1447-1461) written with
+    tensor ops (the same arithmetic as orc.quantize_weight_blocks, which loops
+    over blocks on the CPU). Returns (e4m3 [N,K], scales [N/128, K/128])."""
+    n, k = w_nk.shape
+    blocks = w_nk.view(n // 128, 128, k // 128, 128)
+    scale = (blocks.abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-12)
+    q = (blocks / scale[:, None, :, None]).to(torch.float8_e4m3fn).view(n, k)
+    return q, scale.contiguous()
+
+
+def quant_group_device(x: torch.Tensor, group: int = 128):
+    """orc.quantize_fp8_group with tensor ops on the tensor's own device (cols % group == 0)."""
+    rows, cols = x.shape
+    xf = x.float().view(rows, cols // group, group)
+    sc = (xf.abs().amax(dim=2) / 448.0).clamp_min(1e-12)
+    return (xf / sc[:, :, None]).to(torch.float8_e4m3fn).view(rows, cols), sc.contiguous()
+
+
+def fp8_window_reference(a8, a_s, b8_nk, b_s_nk, rows: slice, cols: slice):
+    """Oracle value (fp32, un-rounded) and noise bound of out[rows, cols] for the
+    [N,K] weight layout; all arguments CPU tensors, cols on 128-column boundaries."""
+    a8w, asw = a8[rows], a_s[rows]
+    b8w = b8_nk[cols]
+    bsw = b_s_nk[cols.start // 128: -(-cols.stop // 128)]
+    ref32 = orc.fp8_gemm_blockwise(a8w, b8w, asw, bsw, 128, 128, "nk", out_dtype=None)
+    noise = accumulation_noise(orc.dequantize_a(a8w, asw).abs(), orc.dequantize_b(b8w, bsw, 128, 128, "nk").abs(),
+                               a8.shape[1])
+    return ref32, noise

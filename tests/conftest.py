@@ -9,6 +9,11 @@ for p in (ROOT, os.path.join(ROOT, "oracle"), os.path.dirname(os.path.abspath(__
         sys.path.insert(0, p)
 
 
+# the tests switch kernels through environment variables between calls; the library
+# otherwise reads them once per process
+os.environ.setdefault("KS_B200_ENV_RELOAD", "1")
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (sm_100a) device; run with -m gpu")
 

@@ -11,7 +11,8 @@ import pytest
 import torch
 
 import ks_oracle as orc
-from _util import accumulation_noise, check_gemm, fp8_inputs, from_bits16, from_u8, gen, golden, w4a16_inputs
+from _util import (accumulation_noise, block_quant_nk_device, check_gemm, fp8_inputs, fp8_window_reference,
+                   from_bits16, from_u8, gen, golden, quant_group_device, w4a16_inputs)
 
 pytestmark = pytest.mark.gpu
 
@@ -84,8 +85,13 @@ def test_fp8_general_kernel(ks, cuda, m, n, k, bn, bk, layout, out_dtype, fp8):
     (200, 336, 400, "kn", 256, torch.float16, "e4m3"),
     (77, 144, 272, "kn", 128, torch.float32, "e5m2"),
     (1, 7168, 512, "nk", 128, torch.bfloat16, "e4m3"),     # decode-like single row
-    (1024, 2048, 7168, "nk", 256, torch.bfloat16, "e4m3"),  # several tiles per CTA, 56 K-blocks
+    (1024, 2048, 7168, "nk", 256, torch.bfloat16, "e4m3"),  # 64 tiles (one per CTA), 56 K-blocks
     (1024, 2048, 7168, "kn", 256, torch.bfloat16, "e4m3"),
+    (2304, 3328, 1024, "nk", 256, torch.bfloat16, "e4m3"),  # 18 x 13 tiles: partial last panel, partial last round
+    (2304, 3328, 1024, "kn", 256, torch.float32, "e4m3"),
+    (2304, 3328, 1024, "nk", 128, torch.bfloat16, "e4m3"),  # 18 x 26 narrow tiles: 3.2 rounds
+    (2500, 2000, 4096, "nk", 256, torch.bfloat16, "e4m3"),  # 160 tiles: 12 left for a K-split round of 8 parts,
+    (2500, 2000, 4096, "kn", 256, torch.float16, "e4m3"),   # among them the ragged last row and column tiles
 ])
 def test_fp8_tcgen05_kernel(ks, cuda, m, n, k, layout, bn_tile, out_dtype, fp8):
     a8, a_s, b8, b_s = fp8_inputs(m, n, k, seed=m * 7 + n + k, fp8=fp8)
@@ -100,31 +106,50 @@ def test_fp8_tcgen05_kernel(ks, cuda, m, n, k, layout, bn_tile, out_dtype, fp8):
         assert orc.rel_frobenius(out, gen_out) < 1e-5
 
 
-@pytest.mark.parametrize("m,n,k,layout,out_dtype,fp8", [
-    (256, 256, 128, "nk", torch.float32, "e4m3"),      # one pair tile, one K-block
-    (256, 256, 128, "kn", torch.float32, "e4m3"),
-    (512, 512, 1024, "nk", torch.bfloat16, "e4m3"),
-    (512, 512, 1024, "kn", torch.bfloat16, "e4m3"),
-    (300, 336, 400, "nk", torch.float16, "e4m3"),      # ragged M, N, K
-    (300, 336, 400, "kn", torch.bfloat16, "e5m2"),
-    (130, 7168, 512, "nk", torch.bfloat16, "e4m3"),    # second CTA of each pair nearly empty
-    (2048, 2048, 7168, "nk", torch.bfloat16, "e4m3"),  # several tiles per pair, 56 K-blocks
-    (2048, 2048, 7168, "kn", torch.bfloat16, "e4m3"),
+
+def _headline_inputs(m, n, k, dev, seed):
+    """Operands of a BASELINE-sized dense problem, made on the device (weights ~N(0, 0.02)
+    block-quantized 128 x 128, activations ~N(0,1) quantized 1 x 128), [N,K] layout."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    a = torch.randn(m, k, generator=g, device=dev).to(torch.bfloat16)
+    a8, a_s = quant_group_device(a)
+    b8, b_s = block_quant_nk_device(torch.randn(n, k, generator=g, device=dev) * 0.02)
+    return a8, a_s, b8, b_s
+
+
+@pytest.mark.parametrize("m,n,k,layout,windows", [
+    # the benchmark's headline problem: 32 x 28 = 896 tiles on 148 CTAs (6.05 rounds)
+    (4096, 7168, 7168, "nk", [(0, 0), (3584, 6144), (1792, 3072)]),
+    (4096, 7168, 7168, "kn", [(3584, 6144), (512, 1024)]),
+    # one K-shard of the row-parallel configuration at 8 GPUs
+    (16384, 8192, 3584, "nk", [(0, 0), (15872, 7168)]),
 ])
-def test_fp8_cta_pair_kernel(ks, cuda, m, n, k, layout, out_dtype, fp8):
-    a8, a_s, b8, b_s = fp8_inputs(m, n, k, seed=m * 3 + n + k, fp8=fp8)
-    ref32, noise = fp8_reference(a8, a_s, b8, b_s)
-    old = os.environ.get("KS_B200_FP8_PAIR")
-    os.environ["KS_B200_FP8_PAIR"] = "1"
-    try:
-        with fp8_path("tcgen05"):
-            out = run_fp8(ks, cuda, a8, a_s, b8, b_s, layout, out_dtype)
-    finally:
-        if old is None:
-            os.environ.pop("KS_B200_FP8_PAIR", None)
-        else:
-            os.environ["KS_B200_FP8_PAIR"] = old
-    check_gemm(out, ref32, noise, f"cta pair {m}x{n}x{k} {layout}")
+def test_fp8_baseline_shapes(ks, cuda, m, n, k, layout, windows):
+    """The full-size problems, default kernel choice. The oracle checks 512 x 1024 windows
+    element by element; the general kernel (the reference kernel's summation order) checks
+    every element of the output on the device."""
+    a8, a_s, b8, b_s = _headline_inputs(m, n, k, cuda, seed=m + n + k)
+    if layout == "kn":
+        b_run, bs_run = b8.t().contiguous(), b_s.t().contiguous()
+    else:
+        b_run, bs_run = b8, b_s
+    out = ks.dispatch.fp8_gemm_blockwise(a8, b_run, a_s, bs_run, b_layout=layout)
+    torch.cuda.synchronize()
+    ks.runtime.stream_synchronize(0)
+    a8c, asc, b8c, bsc = a8.cpu(), a_s.cpu(), b8.cpu(), b_s.cpu()
+    for (r0, c0) in windows:
+        rows, cols = slice(r0, r0 + 512), slice(c0, c0 + 1024)
+        ref32, noise = fp8_window_reference(a8c, asc, b8c, bsc, rows, cols)
+        check_gemm(out[rows, cols].cpu(), ref32, noise, f"{m}x{n}x{k} {layout} window ({r0},{c0})")
+    with fp8_path("general"):
+        full = ks.dispatch.fp8_gemm_blockwise(a8, b_run, a_s, bs_run, b_layout=layout, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+    diff = (out.float() - full).double()
+    frob = float(diff.norm() / full.double().norm())
+    assert frob < 3e-3, f"whole output vs general kernel: {frob}"
+    # nothing worse than bf16 rounding of a correct value anywhere (a wrong tile would be O(1) off)
+    worst = float((diff.abs() / (full.abs().double() + 1e-2 * float(full.abs().max()))).max())
+    assert worst < 0.02, f"worst element vs general kernel: {worst}"
 
 
 def test_fp8_golden(ks, cuda):
@@ -232,6 +257,76 @@ def test_w4a16_tcgen05(ks, cuda, m, k, n, gs, dtype, zeros, bias):
         torch.cuda.synchronize()
     # both kernels multiply the same rounded weights; they differ by summation order only
     assert orc.rel_frobenius(out.cpu().float(), gen_out.cpu().float()) < 2e-3
+
+
+
+@pytest.mark.parametrize("m,k,n,gs,dtype,zeros,bias", [
+    (1, 128, 256, 128, torch.bfloat16, "eight", False),       # one unit
+    (8, 256, 256, 128, torch.bfloat16, "eight", False),
+    (16, 128, 512, 128, torch.bfloat16, "eight", False),
+    (8, 4096, 256, 128, torch.bfloat16, "eight", True),       # one column tile split over 32 CTAs
+    (32, 1024, 2048, 128, torch.bfloat16, "random", False),   # integer zero-points 0..15
+    (32, 1024, 2048, 256, torch.float16, "random", True),     # two K-steps per scale group
+    (5, 512, 208, 128, torch.bfloat16, None, False),          # ragged last column tile, zeros == NULL
+    (64, 512, 384, 128, torch.bfloat16, "eight", False),      # the widest token tile
+    (41, 384, 512, 128, torch.float16, "fraction", False),    # non-integer zero-points: exact fp32 path
+    (9, 640, 1040, 640, torch.bfloat16, "eight", True),       # one group over K, two token groups, ragged N
+    (32, 4096, 28672 // 8, 128, torch.bfloat16, "eight", False),
+    (4, 4096, 14336, 128, torch.bfloat16, "random", False),   # ~12 units per CTA: the ring wraps
+    (16, 7168, 4608, 128, torch.float16, "eight", True),      # 56 K-steps per column tile
+])
+def test_w4a16_decode_kernel(ks, cuda, m, k, n, gs, dtype, zeros, bias):
+    """The register-operand decode kernel against the oracle, twice in a row (the second call
+    finds the split-K counters as the first left them) and against the general kernel."""
+    g = gen(m + k + n)
+    a = torch.randn(m, k, generator=g).to(dtype)
+    codes = torch.randint(0, 16, (k, n), generator=g).to(torch.int32)
+    scales = (torch.randn(k // gs, n, generator=g).mul(0.02).abs() + 1e-3).to(dtype)
+    zp = {"eight": lambda: torch.full((k // gs, n), 8.0).to(dtype),
+          "random": lambda: torch.randint(0, 16, (k // gs, n), generator=g).to(dtype),
+          "fraction": lambda: (torch.rand(k // gs, n, generator=g) * 15).to(dtype),
+          None: lambda: None}[zeros]()
+    b_packed = orc.pack_int4_bytes(codes)
+    bias_t = torch.randn(n, generator=g).to(dtype) if bias else None
+    ref32 = orc.w4a16(a, b_packed, scales, zp, gs, bias_t, out_dtype=None)
+    w = orc.w4a16_weight(b_packed, scales, zp, gs).float()
+    noise = accumulation_noise(a.float().abs(), w.abs(), k)
+    args = (a.to(cuda), b_packed.to(cuda), scales.to(cuda), zp.to(cuda) if zp is not None else None)
+    kw = dict(group_size=gs, bias=bias_t.to(cuda) if bias else None)
+    with w4_path("decode"):
+        out = ks.dispatch.w4a16(*args, **kw)
+        out2 = ks.dispatch.w4a16(*args, **kw)
+        torch.cuda.synchronize()
+        ks.runtime.stream_synchronize(0)
+    check_gemm(out.cpu(), ref32, noise, f"w4a16 decode {m}x{n}x{k}")
+    assert torch.equal(out.cpu().view(torch.int16), out2.cpu().view(torch.int16)), "not reproducible run to run"
+    with w4_path("general"):
+        gen_out = ks.dispatch.w4a16(*args, **kw)
+        torch.cuda.synchronize()
+    assert orc.rel_frobenius(out.cpu().float(), gen_out.cpu().float()) < 2e-3
+
+
+@pytest.mark.parametrize("k,n", [(4096, 28672), (14336, 4096)])
+def test_w4a16_baseline_shapes(ks, cuda, k, n):
+    """The decode sweep of the benchmark (Llama-3-8B MLP shapes, M in {1, 8, 32, 128}), default
+    kernel choice; the oracle checks three windows of 1024 columns (first, middle, last)."""
+    g = gen(k + n)
+    codes_b = torch.randint(0, 256, (k // 2, n), generator=g, dtype=torch.uint8)     # code = q + 8, q uniform
+    scales = (torch.randn(k // 128, n, generator=g).mul(0.02).abs() + 1e-3).to(torch.bfloat16)
+    zeros = torch.full((k // 128, n), 8.0).to(torch.bfloat16)
+    bp_d, sc_d, zp_d = codes_b.to(cuda), scales.to(cuda), zeros.to(cuda)
+    windows = [slice(0, 1024), slice(n // 2 - 256, n // 2 + 768), slice(n - 1024, n)]
+    wref = [(orc.w4a16_weight(codes_b[:, w], scales[:, w], zeros[:, w], 128).float()) for w in windows]
+    for m in (1, 8, 32, 128):
+        a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+        out = ks.dispatch.w4a16(a.to(cuda), bp_d, sc_d, zp_d, group_size=128)
+        torch.cuda.synchronize()
+        ks.runtime.stream_synchronize(0)
+        out = out.cpu()
+        for w, wf in zip(windows, wref):
+            ref32 = a.float() @ wf
+            noise = accumulation_noise(a.float().abs(), wf.abs(), k)
+            check_gemm(out[:, w], ref32, noise, f"w4a16 M={m} K={k} N={n} columns {w.start}..{w.stop}")
 
 
 @pytest.mark.parametrize("operand", ["smem", "tmem"])
@@ -386,3 +481,40 @@ def test_grouped_gemm_fp8_blockwise(ks, cuda, layout, path, n, k):
         ks.runtime.stream_synchronize(0)
     noise = torch.full_like(ref32, float(ref32.abs().max()) * 1e-5)
     check_gemm(out.cpu(), ref32, noise, f"grouped fp8 {layout} {path}")
+
+
+@pytest.mark.parametrize("n,k", [(4096, 7168), (7168, 2048)])
+def test_grouped_gemm_fp8_256_experts(ks, cuda, n, k):
+    """The MoE configuration's expert count and GEMM sizes: 256 experts, rows per expert from a
+    top-8 routing of 4096 tokens (ragged), experts 3 and 200 emptied. The oracle checks the rows
+    of four experts; weights are made on the device, one expert at a time."""
+    e = 256
+    gr = gen(17)
+    _, ids = orc.moe_route(torch.randn(4096, e, generator=gr), 8)
+    counts = torch.bincount(ids.reshape(-1), minlength=e)
+    counts[3] = 0
+    counts[200] = 0
+    offs = torch.zeros(e + 1, dtype=torch.int32)
+    offs[1:] = torch.cumsum(counts, 0).to(torch.int32)
+    total = int(offs[-1])
+    gd = torch.Generator(device=cuda).manual_seed(n + k)
+    a = torch.randn(total, k, generator=gd, device=cuda).to(torch.bfloat16)
+    a8, a_s = quant_group_device(a)
+    b8 = torch.empty(e, n, k, dtype=torch.float8_e4m3fn, device=cuda)
+    b_s = torch.empty(e, n // 128, k // 128, dtype=torch.float32, device=cuda)
+    for i in range(e):
+        b8[i], b_s[i] = block_quant_nk_device(torch.randn(n, k, generator=gd, device=cuda) * 0.02)
+    out = ks.dispatch.moe(a8, b8, offs.to(cuda), num_experts=e, n=n, k=k, a_scale=a_s, b_scale=b_s, b_layout="nk")
+    torch.cuda.synchronize()
+    ks.runtime.stream_synchronize(0)
+    biggest = int(torch.argmax(counts))
+    for i in (0, 2, biggest, e - 1):
+        lo, hi = int(offs[i]), int(offs[i + 1])
+        if hi == lo:
+            continue
+        a8c, asc, b8c, bsc = a8[lo:hi].cpu(), a_s[lo:hi].cpu(), b8[i].cpu(), b_s[i].cpu()
+        ref32 = orc.fp8_gemm_blockwise(a8c, b8c, asc, bsc, 128, 128, "nk", out_dtype=None)
+        noise = accumulation_noise(orc.dequantize_a(a8c, asc).abs(), orc.dequantize_b(b8c, bsc, 128, 128, "nk").abs(), k)
+        check_gemm(out[lo:hi].cpu(), ref32, noise, f"256 experts, expert {i} ({hi - lo} rows) n={n} k={k}")
+    # rows of the emptied experts do not exist; the row after them belongs to the next expert
+    assert int(offs[4]) == int(offs[3]) and int(offs[201]) == int(offs[200])
