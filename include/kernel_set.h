@@ -6,4 +6,5 @@
 #include "kernel_set/gemm.h"
 #include "kernel_set/quant.h"
 #include "kernel_set/moe.h"
+#include "kernel_set/activation.h"
 #endif /* KERNEL_SET_H_ */

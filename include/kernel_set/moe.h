@@ -1,10 +1,14 @@
 /*
- * Grouped (per-expert) GEMM over rows already sorted by expert.
+ * Mixture-of-experts layer: softmax top-k gate, the permutation that sorts
+ * (token, slot) pairs by expert, row gather / weighted scatter, and the
+ * grouped (per-expert) GEMMs over rows sorted by expert.
  *
- * Replaces ks_moe_grouped_gemm of include/kernel_set/moe.h:57-65 of the
- * reference project and adds the FP8 block-scaled form that the reference
- * only reaches through external providers. Gating and permutation kernels of
- * that header are not exported here.
+ * Replaces ks_moe_gate_softmax_topk, ks_moe_compute_permutation,
+ * ks_moe_permute, ks_moe_unpermute and ks_moe_grouped_gemm of
+ * include/kernel_set/moe.h:14-65 of the reference project, and adds the FP8
+ * forms (block-scaled grouped GEMM, gather fused with the 1 x 128 quantizer)
+ * that the reference only reaches through external providers. The sigmoid
+ * group-limited gate of that header (moe.h:25-31) is not exported here.
  */
 #ifndef KERNEL_SET_MOE_H_
 #define KERNEL_SET_MOE_H_
@@ -12,6 +16,91 @@
 #include "kernel_set/types.h"
 
 KS_BEGIN_EXTERN_C
+
+/*
+ * Softmax over the experts, then the top_k largest probabilities.
+ *   logits       [num_tokens, num_experts]  f32 / f16 / bf16 (`dtype`)
+ *   out_weights  [num_tokens, top_k]  fp32, descending; divided by their sum
+ *                                     when `renormalize` is non-zero
+ *   out_indices  [num_tokens, top_k]  int32 expert ids; among equal
+ *                                     probabilities the lowest id comes first
+ * At most 1024 experts and top_k 32 (UNSUPPORTED_SHAPE beyond), as the
+ * reference. Same contract as the reference: moe.h:14-23, moe_gate.cu:43-119.
+ */
+KS_API ks_status_t ks_moe_gate_softmax_topk(float* out_weights,
+                                            int32_t* out_indices,
+                                            const void* logits,
+                                            int64_t num_tokens,
+                                            int num_experts, int top_k,
+                                            int renormalize, ks_dtype_t dtype,
+                                            ks_stream_t stream);
+
+/*
+ * Counting sort of the routed pairs by expert.
+ *   topk_indices      [num_tokens, top_k]  int32
+ *   sorted_token_ids  [num_tokens*top_k]   int32: pair ids (token*top_k + slot)
+ *                                          grouped by expert
+ *   expert_offsets    [num_experts+1]      int32 group boundaries
+ * The sort is stable (pairs of one expert keep their order), where the
+ * reference leaves the order inside a group unspecified; pairs whose expert id
+ * is out of range are dropped and the unused tail of sorted_token_ids is
+ * filled with -1. One launch, no allocation, no synchronisation (the
+ * reference does all three per call, moe_permute.cu:205-242).
+ * Same contract otherwise: moe.h:33-40.
+ */
+KS_API ks_status_t ks_moe_compute_permutation(int32_t* sorted_token_ids,
+                                              int32_t* expert_offsets,
+                                              const int32_t* topk_indices,
+                                              int64_t num_tokens,
+                                              int num_experts, int top_k,
+                                              ks_stream_t stream);
+
+/*
+ * permuted[r, :] = input[sorted_token_ids[r] / top_k, :]; rows whose id is
+ * negative or out of range are zero-filled.
+ *   input [num_tokens, hidden], permuted [num_tokens*top_k, hidden], any of
+ *   f32 / f16 / bf16 / e4m3 / e5m2.
+ * Same contract as the reference: moe.h:42-47, moe_permute.cu:107-127.
+ */
+KS_API ks_status_t ks_moe_permute(void* permuted, const void* input,
+                                  const int32_t* sorted_token_ids,
+                                  int64_t num_tokens, int top_k,
+                                  int64_t hidden, ks_dtype_t dtype,
+                                  ks_stream_t stream);
+
+/*
+ * ks_moe_permute fused with ks_quantize_fp8_group(group_size = 128): row r of
+ * the output holds the fp8 codes and the 1 x 128 scales of input row
+ * sorted_token_ids[r] / top_k, bit-identical to running the two calls one
+ * after the other, without the 16-bit intermediate.
+ *   out_fp8 [num_tokens*top_k, hidden], out_scale [num_tokens*top_k, hidden/128]
+ * hidden must be a multiple of 128. No counterpart in the reference.
+ */
+KS_API ks_status_t ks_moe_permute_quant_fp8(void* out_fp8, float* out_scale,
+                                            const void* input,
+                                            const int32_t* sorted_token_ids,
+                                            int64_t num_tokens, int top_k,
+                                            int64_t hidden,
+                                            ks_dtype_t in_dtype,
+                                            ks_dtype_t fp8_dtype,
+                                            ks_stream_t stream);
+
+/*
+ * out[t, :] = sum over slots k of routing_weights[t, k] * permuted[row of
+ * pair (t, k), :], slots added in order in fp32, one rounding at the end.
+ *   permuted [num_tokens*top_k, hidden], out [num_tokens, hidden], f32/f16/bf16
+ *   routing_weights [num_tokens, top_k] fp32
+ * The inverse permutation lives in a library-owned, stream-ordered buffer
+ * (first use of a stream allocates it; do that before any stream capture); the
+ * reference allocates, synchronises and frees per call
+ * (moe_permute.cu:317-375). Same contract otherwise: moe.h:49-56.
+ */
+KS_API ks_status_t ks_moe_unpermute(void* out, const void* permuted,
+                                    const int32_t* sorted_token_ids,
+                                    const float* routing_weights,
+                                    int64_t num_tokens, int top_k,
+                                    int64_t hidden, ks_dtype_t dtype,
+                                    ks_stream_t stream);
 
 /*
  * For every expert e: C[off_e : off_{e+1}, :] = A[off_e : off_{e+1}, :] . B[e]

@@ -170,10 +170,20 @@ _decl("ks_dequantize_int4", [_VP, _VP, _VP, _VP, c_int64, c_int64, c_int, c_int,
 _decl("ks_repack_int4", [_VP, _VP, _VP, c_int64, c_int64, c_int, _VP])
 
 # moe.h
+_decl("ks_moe_gate_softmax_topk", [POINTER(c_float), POINTER(c_int32), _VP, c_int64, c_int, c_int, c_int, c_int, _VP])
+_decl("ks_moe_compute_permutation", [POINTER(c_int32), POINTER(c_int32), POINTER(c_int32), c_int64, c_int, c_int, _VP])
+_decl("ks_moe_permute", [_VP, _VP, POINTER(c_int32), c_int64, c_int, c_int64, c_int, _VP])
+_decl("ks_moe_permute_quant_fp8", [_VP, POINTER(c_float), _VP, POINTER(c_int32), c_int64, c_int, c_int64, c_int, c_int, _VP])
+_decl("ks_moe_unpermute", [_VP, _VP, POINTER(c_int32), POINTER(c_float), c_int64, c_int, c_int64, c_int, _VP])
 _decl("ks_moe_grouped_gemm", [_VP, _VP, _VP, POINTER(c_int32), c_int, c_int64, c_int64, c_int64, c_int, _VP])
 _decl("ks_moe_grouped_gemm_fp8_blockwise",
       [_VP, _VP, _VP, POINTER(c_float), POINTER(c_float), POINTER(c_int32), c_int, c_int64, c_int64, c_int64,
        c_int, c_int, c_int, c_int, c_int, _VP])
+
+# activation.h
+_decl("ks_swiglu", [_VP, _VP, _VP, c_int64, c_int64, c_int, _VP])
+_decl("ks_swiglu_packed", [_VP, _VP, c_int64, c_int64, c_int, _VP])
+_decl("ks_swiglu_packed_quant_fp8", [_VP, POINTER(c_float), _VP, c_int64, c_int64, c_int, c_int, _VP])
 
 
 def status_string(status: int) -> str:

@@ -17,6 +17,7 @@
 // plus 4/128 for the scale.
 #include "common.cuh"
 #include "kernel_set/quant.h"
+#include "quant_math.cuh"
 
 #ifndef KSB_QUANT_SEGS
 #define KSB_QUANT_SEGS 1
@@ -25,96 +26,7 @@
 namespace ksb {
 namespace {
 
-constexpr float kScaleFloor = 1e-12f;
-
-template <typename T> struct Vec16;  // 16 elements of T as fp32
-
-template <> struct Vec16<__nv_bfloat16> {
-  __device__ static void load(const __nv_bfloat16* p, float (&v)[16]) {
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
-    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      v[2 * i] = __uint_as_float(w[i] << 16);
-      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-  }
-};
-template <> struct Vec16<__half> {
-  __device__ static void load(const __half* p, float (&v)[16]) {
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
-    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-      v[2 * i] = f.x;
-      v[2 * i + 1] = f.y;
-    }
-  }
-};
-template <> struct Vec16<float> {
-  __device__ static void load(const float* p, float (&v)[16]) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float4 f = __ldg(reinterpret_cast<const float4*>(p) + i);
-      v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
-    }
-  }
-};
-
-// Two fp32 -> two fp8 codes (low byte = first value), RNE, saturating.
-template <bool E5M2>
-__device__ __forceinline__ uint32_t cvt_pair(float lo, float hi) {
-  return __nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, E5M2 ? __NV_E5M2 : __NV_E4M3);
-}
-template <bool E5M2>
-__device__ __forceinline__ uint8_t cvt_one(float v) {
-  return __nv_cvt_float_to_fp8(v, __NV_SATFINITE, E5M2 ? __NV_E5M2 : __NV_E4M3);
-}
-
-// One 16-element segment of a group: maximum over the 8-lane segment, scale, codes.
-template <typename T, bool E5M2>
-__device__ __forceinline__ void quant_segment(uint8_t* __restrict__ out, float* __restrict__ scale, const float (&v)[16],
-                                              int64_t seg, bool live, float qmax) {
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  // All 32 lanes take part in the shuffles; a dead tail segment carries 0.
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  if (!live) return;
-  const float sc = fmaxf(__fdiv_rn(amax, qmax), kScaleFloor);
-  if ((threadIdx.x & 7) == 0) scale[seg >> 3] = sc;
-  // x / sc, correctly rounded, without sixteen IEEE divisions: with r = RN(1/sc) and
-  // q0 = RN(x*r) (within one ulp of the quotient), the residual e = x - q0*sc is exact in
-  // an FMA and RN(q0 + e*r) is the correctly rounded quotient (Markstein's correction
-  // step, the tail of the division routine itself). Valid while nothing overflows or
-  // goes subnormal on the way; scales outside [1e-30, 1e30] take the division.
-  float q[16];
-  if (sc > 1e-30f && sc < 1e30f) {
-    const float r = __frcp_rn(sc);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float q0 = __fmul_rn(v[i], r);
-      const float e = __fmaf_rn(-q0, sc, v[i]);
-      q[i] = __fmaf_rn(e, r, q0);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) q[i] = __fdiv_rn(v[i], sc);
-  }
-  uint32_t w[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t p0 = cvt_pair<E5M2>(q[4 * i], q[4 * i + 1]);
-    const uint32_t p1 = cvt_pair<E5M2>(q[4 * i + 2], q[4 * i + 3]);
-    w[i] = (p0 & 0xffffu) | (p1 << 16);
-  }
-  __stcs(reinterpret_cast<uint4*>(out + seg * 16), make_uint4(w[0], w[1], w[2], w[3]));
-}
+using namespace quantmath;
 
 // A thread owns kSegs segments, all loaded before the first is used. Measured on B200 for
 // [4096, 7168] bf16: 22 us with one segment per thread, 25 us with two, 35 us with four

@@ -16,7 +16,7 @@
 // (tcgen05.st at ~80 B/clk per SM plus two more barrier hops per unit). A
 // register-operand mma.sync takes the dequantised pairs where they are made.
 //
-// One CTA per SM, 8 warps, no producer warp and no spin-wait anywhere:
+// Two CTAs per SM of 8 warps each, no producer warp and no spin-wait anywhere:
 //   * all threads copy unit u+S-1 with cp.async (16 B each, rows of 256 contiguous
 //     bytes of the packed matrix = 256 weight columns x 64 byte-rows = 128 k;
 //     plus the unit's activation slice and its scale / zero-point rows) into a
@@ -36,9 +36,10 @@
 //     instructions for up to 8*MG tokens.
 // Work is cut stream-K style: (column tile, K-step) units are dealt to the CTAs
 // in equal contiguous runs. A tile shared by several CTAs is finished per WARP:
-// every warp writes its fp32 partial (32 columns) to its slot, bumps the counter
-// of (tile, warp) and the warp that completes the count adds the slots in slot
-// order (run-to-run reproducible) and writes C. No CTA ever waits for another.
+// every warp writes its fp32 partial (32 columns) to its slot and, once its CTA's
+// run is over and no copy is in flight, bumps the counter of (tile, warp); the warp
+// that completes the count adds the slots in slot order (run-to-run reproducible)
+// and writes C. No CTA ever waits for another.
 //
 // Roofline: HBM-bound; algorithmic bytes per launch
 // K*N/2 + (K/gs)*N*2*(1 or 2) + M*K*2 + M*N*2.
@@ -66,10 +67,14 @@ struct Cfg {
   static constexpr int kXBytes = kTokens * kStepK * 2;   // activation slice of the unit
   static constexpr int kSZBytes = 2 * kTileN * 2;        // one row of scales, one of zero-points
   static constexpr int kStageBytes = kWBytes + kXBytes + kSZBytes;
-  static constexpr int kStages = MG <= 4 ? 8 : 6;
+  // Two CTAs per SM (16 warps) up to 32 tokens: a warp spends about half of its time
+  // between dependent instructions, and the __syncthreads of one CTA overlaps the other's
+  // work. Their rings together keep 100+ KB of copies in flight per SM.
+  static constexpr int kCtasPerSm = MG <= 4 ? 2 : 1;
+  static constexpr int kStages = MG <= 2 ? 5 : (MG == 4 ? 4 : 6);
   static constexpr int kSmemBytes = kStages * kStageBytes + 128;
   static constexpr int kAccRegs = MG * 2 * 4;            // per lane: token groups x column chunks x 4
-  static_assert(kSmemBytes <= 232448, "stage ring exceeds the shared memory a CTA can opt in to");
+  static_assert(kSmemBytes * kCtasPerSm + 1024 * kCtasPerSm <= 233472, "stage rings exceed the shared memory of an SM");
 };
 
 struct Params {
@@ -173,7 +178,7 @@ __device__ __forceinline__ uint32_t w_chunk(uint32_t cc, uint32_t row) { return 
 __device__ __forceinline__ uint32_t x_chunk(uint32_t cc, uint32_t tok) { return cc ^ ((tok & 3u) << 1); }
 
 template <typename T, int MG>
-__global__ void __launch_bounds__(kThreads, 1) w4a16_decode_kernel(const Params p) {
+__global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_kernel(const Params p) {
   using C = Cfg<MG>;
   using P16 = Pack16<T>;
   using V2 = typename P16::V2;
@@ -192,49 +197,66 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_decode_kernel(const Params 
   const int n_units = static_cast<int>(u_end - u_begin);
 
   // ------------------------------ loader state ------------------------------
+  // Every thread copies the same chunks of every unit: 16-byte chunk cc of byte-rows
+  // r0, r0 + 16, r0 + 32, r0 + 48 of the packed tile, chunk cc of token rows r0, r0 + 16, ...
+  // of the activation slice, and (warps 0 and 1) chunk `lane` of the scale / zero-point row.
+  // Source pointers advance by a constant per K-step and are rebuilt when the tile changes.
   int tile_l = static_cast<int>(u_begin / p.k_steps);
   int step_l = static_cast<int>(u_begin - static_cast<long long>(tile_l) * p.k_steps);
+  int grp_l = step_l / p.gs_steps, in_grp_l = step_l - grp_l * p.gs_steps;
   int loaded = 0;
-  const uint8_t* a_bytes = static_cast<const uint8_t*>(p.a);
+  const uint32_t ld_r0 = tid >> 4, ld_cc = tid & 15u;
+  const uint32_t w_dst = ld_r0 * kTileN + (w_chunk(ld_cc, ld_r0) << 4);
+  const uint32_t x_dst = kWBytes + ld_r0 * (kStepK * 2) + (x_chunk(ld_cc, ld_r0) << 4);
+  const size_t w_row16 = static_cast<size_t>(16) * p.n;            // 16 byte-rows further down
+  const size_t w_step = static_cast<size_t>(kRows) * p.n;          // one K-step further down
+  const size_t x_row16 = static_cast<size_t>(16) * p.k * 2;        // 16 tokens further down
+  const uint8_t* const a_bytes = static_cast<const uint8_t*>(p.a);
+  const uint8_t* const sz_base = static_cast<const uint8_t*>(warp == 0 ? p.scales : p.zeros);
+  const bool sz_active = warp == 0 || (warp == 1 && p.has_zeros);
+  const uint32_t sz_dst = kWBytes + C::kXBytes + (warp == 1 ? kTileN * 2 : 0) + (lane << 4);
+  const uint8_t* w_src;
+  const uint8_t* x_src = a_bytes + (static_cast<size_t>(ld_r0) * p.k + ld_cc * 8) * 2 + static_cast<size_t>(step_l) * (kStepK * 2);
+  const uint8_t* sz_src;
+  uint32_t w_bytes, sz_bytes;
+  auto enter_tile = [&](int tile, int step, int grp) {
+    const int col0 = tile * kTileN;
+    const bool w_ok = col0 + static_cast<int>(ld_cc) * 16 < p.n;
+    w_bytes = w_ok ? 16u : 0u;
+    w_src = w_ok ? p.w + (static_cast<size_t>(step) * kRows + ld_r0) * p.n + col0 + ld_cc * 16 : p.w;
+    const bool s_ok = sz_active && col0 + lane * 8 < p.n;
+    sz_bytes = s_ok ? 16u : 0u;
+    sz_src = s_ok ? sz_base + (static_cast<size_t>(grp) * p.n + col0 + lane * 8) * 2 : a_bytes;
+  };
+  enter_tile(tile_l, step_l, grp_l);
   auto issue = [&]() {
     if (loaded < n_units) {
       const uint32_t st = ring + static_cast<uint32_t>(loaded % S) * C::kStageBytes;
-      const int col0 = tile_l * kTileN;
-      // packed weight: 64 byte-rows x 16 chunks, 16 consecutive lanes read one 256-byte row
-      const uint8_t* wsrc = p.w + static_cast<size_t>(step_l) * kRows * p.n + col0;
 #pragma unroll
-      for (int i = 0; i < (kRows * 16) / kThreads; ++i) {
-        const uint32_t c = tid + kThreads * i;
-        const uint32_t row = c >> 4, cc = c & 15u;
-        const bool ok = col0 + static_cast<int>(cc) * 16 < p.n;
-        const uint8_t* src = ok ? wsrc + static_cast<size_t>(row) * p.n + cc * 16 : p.w;
-        cp_async16(st + row * kTileN + (w_chunk(cc, row) << 4), src, ok ? 16u : 0u);
-      }
-      // activations of this K-step: kTokens rows x 16 chunks (8 elements each)
+      for (int i = 0; i < 4; ++i)
+        cp_async16(st + w_dst + i * (16 * kTileN), w_bytes ? w_src + i * w_row16 : w_src, w_bytes);
 #pragma unroll
-      for (int i = 0; i < (C::kTokens * 16 + kThreads - 1) / kThreads; ++i) {
-        const uint32_t c = tid + kThreads * i;
-        if (C::kTokens * 16 >= kThreads * (i + 1) || c < C::kTokens * 16) {
-          const uint32_t tok = c >> 4, cc = c & 15u;
-          const bool ok = static_cast<int>(tok) < p.m;
-          const uint8_t* src = ok ? a_bytes + (static_cast<size_t>(tok) * p.k + step_l * kStepK + cc * 8) * 2 : a_bytes;
-          cp_async16(st + kWBytes + tok * (kStepK * 2) + (x_chunk(cc, tok) << 4), src, ok ? 16u : 0u);
+      for (int i = 0; i < (C::kTokens + 15) / 16; ++i) {
+        const int tok = static_cast<int>(ld_r0) + 16 * i;
+        if (tok < C::kTokens) {
+          const bool ok = tok < p.m;
+          cp_async16(st + x_dst + i * (16 * kStepK * 2), ok ? x_src + i * x_row16 : a_bytes, ok ? 16u : 0u);
         }
       }
-      // the group's scales (and zero-points): 32 chunks of 8 elements each
-      if (tid < 64) {
-        const int which = tid >> 5;
-        const uint32_t cc = tid & 31u;
-        if (which == 0 || p.has_zeros) {
-          const uint8_t* base = static_cast<const uint8_t*>(which ? p.zeros : p.scales);
-          const bool ok = col0 + static_cast<int>(cc) * 8 < p.n;
-          const uint8_t* src =
-              ok ? base + (static_cast<size_t>(step_l / p.gs_steps) * p.n + col0 + cc * 8) * 2 : base;
-          cp_async16(st + kWBytes + C::kXBytes + which * (kTileN * 2) + (cc << 4), src, ok ? 16u : 0u);
-        }
-      }
+      if (sz_active) cp_async16(st + sz_dst, sz_src, sz_bytes);
       ++loaded;
-      if (++step_l == p.k_steps) { step_l = 0; ++tile_l; }
+      if (++step_l == p.k_steps) {
+        step_l = 0; grp_l = 0; in_grp_l = 0; ++tile_l;
+        x_src -= static_cast<size_t>(p.k_steps - 1) * (kStepK * 2);
+        enter_tile(tile_l, 0, 0);
+      } else {
+        x_src += kStepK * 2;
+        if (w_bytes) w_src += w_step;
+        if (++in_grp_l == p.gs_steps) {
+          in_grp_l = 0; ++grp_l;
+          if (sz_bytes) sz_src += static_cast<size_t>(p.n) * 2;
+        }
+      }
     }
     cp_async_commit();
   };
@@ -251,16 +273,48 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_decode_kernel(const Params 
   int tile = static_cast<int>(u_begin / p.k_steps);
   int step = static_cast<int>(u_begin - static_cast<long long>(tile) * p.k_steps);
   int seg_first_step = step;
+  // partial segments of this run (at most two: the head of the run and its tail), published
+  // after the main loop
+  int pub_tile[2] = {-1, -1};
+  int n_pub = 0;
 
   // lane's row address inside a stage for ldmatrix: matrix mi = lane / 8 covers K-block
   // (mi / 2) of the pair and column chunk (mi % 2) of this warp; row = lane % 8
   const uint32_t ld_mi = lane >> 3, ld_i = lane & 7u;
   const uint32_t ld_off = (8u * (ld_mi >> 1) + ld_i) * kTileN + (w_chunk(2u * warp + (ld_mi & 1u), ld_i) << 4);
-  // lane's 8 bytes of an activation row: token 8*tg + g, k = 16*kb + 4*s .. +3
+  // lane's 8 bytes of an activation row: token 8*tg + g, k = 16*kb + 4*s .. +3; all tokens
+  // 8t + g of a lane share g % 4, hence the chunk swizzle
   const uint32_t x_row_off = kWBytes + static_cast<uint32_t>(g) * (kStepK * 2) + 8u * (s & 1u);
+  const uint32_t x_swz = (static_cast<uint32_t>(g) & 3u) << 1;
+  const uint32_t sz_off = kWBytes + C::kXBytes + (32u * warp + 2u * g) * 2u;
   const V2 magic2 = P16::splat(P16::kMagic);
   T* cmat = static_cast<T*>(p.c);
   const T* bias = static_cast<const T*>(p.bias);
+  constexpr int kSlotFloats = C::kAccRegs * 32;
+  const size_t part_stride = static_cast<size_t>(kWarps) * kSlotFloats;
+
+  auto store_c = [&](float (&v)[MG][2][4], int tile_of) {
+    const int n_base = tile_of * kTileN + 32 * warp + 2 * g;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int n = n_base + 16 * c;
+      if (n < p.n) {   // N is a multiple of 16 and n is even: n + 1 is inside too
+        const float b0 = bias != nullptr ? to_f32<T>(bias[n]) : 0.f;
+        const float b1 = bias != nullptr ? to_f32<T>(bias[n + 1]) : 0.f;
+#pragma unroll
+        for (int t = 0; t < MG; ++t) {
+          const int tok = 8 * t + 2 * s;
+          // d0 (n, tok) d1 (n, tok+1) d2 (n+1, tok) d3 (n+1, tok+1)
+          if (tok < p.m)
+            *reinterpret_cast<uint32_t*>(cmat + static_cast<size_t>(tok) * p.n + n) =
+                P16::make(v[t][c][0] + b0, v[t][c][2] + b1);
+          if (tok + 1 < p.m)
+            *reinterpret_cast<uint32_t*>(cmat + static_cast<size_t>(tok + 1) * p.n + n) =
+                P16::make(v[t][c][1] + b0, v[t][c][3] + b1);
+        }
+      }
+    }
+  };
 
 #pragma unroll 1
   for (int i = 0; i < S - 1; ++i) issue();
@@ -278,137 +332,86 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_decode_kernel(const Params 
     uint32_t bad = 0u;
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
-      const uint32_t off = kWBytes + C::kXBytes + (32u * warp + 16u * c + 2u * g) * 2u;
-      sraw[c] = lds32(st + off);
-      zraw[c] = p.has_zeros ? lds32(st + off + kTileN * 2) : 0u;
+      sraw[c] = lds32(st + sz_off + 32u * c);
+      zraw[c] = p.has_zeros ? lds32(st + sz_off + 32u * c + kTileN * 2) : 0u;
       sc[c][0] = P16::from_bits(__byte_perm(sraw[c], sraw[c], 0x1010));
       sc[c][1] = P16::from_bits(__byte_perm(sraw[c], sraw[c], 0x3232));
-      const uint32_t z0 = __byte_perm(zraw[c], zraw[c], 0x1010), z1 = __byte_perm(zraw[c], zraw[c], 0x3232);
-      zz[c][0] = __hadd2(P16::from_bits(z0), magic2);
-      zz[c][1] = __hadd2(P16::from_bits(z1), magic2);
-      // (magic + zero) exact and |q - zero| exact: non-negative integer zero-points up to kMaxZero
-      bad |= (P16::bits(__hsub2(zz[c][0], magic2)) ^ z0) | (P16::bits(__hsub2(zz[c][1], magic2)) ^ z1);
-      bad |= zraw[c] & 0x80008000u;
-      bad |= ((zraw[c] & 0xFFFFu) > P16::kMaxZeroBits || (zraw[c] >> 16) > P16::kMaxZeroBits) ? 1u : 0u;
+      // (magic + zero) must be exact; then (magic + q) - (magic + zero) is exact too: true for
+      // every non-negative integer zero-point that survives the round trip
+      const V2 zp = __hadd2(P16::from_bits(zraw[c]), magic2);
+      bad |= (P16::bits(__hsub2(zp, magic2)) ^ zraw[c]) | (zraw[c] & 0x80008000u);
+      const uint32_t zb = P16::bits(zp);
+      zz[c][0] = P16::from_bits(__byte_perm(zb, zb, 0x1010));
+      zz[c][1] = P16::from_bits(__byte_perm(zb, zb, 0x3232));
     }
     const bool simple = !__any_sync(0xFFFFFFFFu, bad != 0u);
 
-    auto unit_body = [&](auto fast_tag) {
+    auto pair_body = [&](int pr, auto fast_tag) {
       constexpr bool kFast = decltype(fast_tag)::value;
+      uint32_t r[4];
+      ldmatrix_x4_trans(r, st + ld_off + pr * (16 * kTileN));
 #pragma unroll
-      for (int pr = 0; pr < 4; ++pr) {
-        uint32_t r[4];
-        ldmatrix_x4_trans(r, st + ld_off + pr * (16 * kTileN));
+      for (int kbi = 0; kbi < 2; ++kbi) {
+        const int kb = 2 * pr + kbi;
+        uint32_t b[MG][2];
 #pragma unroll
-        for (int kbi = 0; kbi < 2; ++kbi) {
-          const int kb = 2 * pr + kbi;
-          uint32_t b[MG][2];
+        for (int t = 0; t < MG; ++t) {
+          const uint2 x = lds64(st + x_row_off + t * (8 * kStepK * 2) + (((2u * kb + (s >> 1)) ^ x_swz) << 4));
+          b[t][0] = __byte_perm(x.x, x.y, 0x5410);   // k = 4s, 4s+2
+          b[t][1] = __byte_perm(x.x, x.y, 0x7632);   // k = 4s+1, 4s+3
+        }
 #pragma unroll
-          for (int t = 0; t < MG; ++t) {
-            // all tokens 8t + g of a lane share g % 4, hence the chunk swizzle
-            const uint2 x = lds64(st + x_row_off + t * (8 * kStepK * 2) +
-                                  (x_chunk(2u * kb + (s >> 1), static_cast<uint32_t>(g)) << 4));
-            b[t][0] = __byte_perm(x.x, x.y, 0x5410);   // k = 4s, 4s+2
-            b[t][1] = __byte_perm(x.x, x.y, 0x7632);   // k = 4s+1, 4s+3
-          }
+        for (int c = 0; c < 2; ++c) {
+          const uint32_t w = r[kbi * 2 + c];
+          // bytes of w: (row 2s, n 2g) (row 2s, n 2g+1) (row 2s+1, n 2g) (row 2s+1, n 2g+1);
+          // low nibble = even k of the row, high nibble = odd k
+          const uint32_t q[4] = {w & 0x000F000Fu, (w >> 8) & 0x000F000Fu, (w >> 4) & 0x000F000Fu,
+                                 (w >> 12) & 0x000F000Fu};
+          uint32_t a[4];
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            const uint32_t w = r[kbi * 2 + c];
-            // bytes of w: (row 2s, n 2g) (row 2s, n 2g+1) (row 2s+1, n 2g) (row 2s+1, n 2g+1);
-            // low nibble = even k of the row, high nibble = odd k
-            const uint32_t q[4] = {w & 0x000F000Fu, (w >> 8) & 0x000F000Fu, (w >> 4) & 0x000F000Fu,
-                                   (w >> 12) & 0x000F000Fu};
-            uint32_t a[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if constexpr (kFast) {
-                a[j] = P16::bits(__hmul2(__hsub2(P16::from_bits(q[j] | P16::kMagic2), zz[c][j & 1]), sc[c][j & 1]));
-              } else {
-                // zero-points that are not small integers: the fp32 statement, verbatim
-                const uint32_t sh = (j & 1) ? 16u : 0u;
-                const float zf = P16::to_float((zraw[c] >> sh) & 0xFFFFu), sf = P16::to_float((sraw[c] >> sh) & 0xFFFFu);
-                a[j] = P16::make(__fmul_rn(__fsub_rn(static_cast<float>(q[j] & 15u), zf), sf),
-                                 __fmul_rn(__fsub_rn(static_cast<float>(q[j] >> 16), zf), sf));
-              }
+          for (int j = 0; j < 4; ++j) {
+            if constexpr (kFast) {
+              a[j] = P16::bits(__hmul2(__hsub2(P16::from_bits(q[j] | P16::kMagic2), zz[c][j & 1]), sc[c][j & 1]));
+            } else {
+              // zero-points that are not small integers: the fp32 statement, verbatim
+              const uint32_t sh = (j & 1) ? 16u : 0u;
+              const float zf = P16::to_float((zraw[c] >> sh) & 0xFFFFu), sf = P16::to_float((sraw[c] >> sh) & 0xFFFFu);
+              a[j] = P16::make(__fmul_rn(__fsub_rn(static_cast<float>(q[j] & 15u), zf), sf),
+                               __fmul_rn(__fsub_rn(static_cast<float>(q[j] >> 16), zf), sf));
             }
-#pragma unroll
-            for (int t = 0; t < MG; ++t) P16::mma(acc[t][c], a, b[t]);
           }
+#pragma unroll
+          for (int t = 0; t < MG; ++t) P16::mma(acc[t][c], a, b[t]);
         }
       }
     };
-    if (simple) unit_body(std::true_type{}); else unit_body(std::false_type{});
+    if (simple) {
+#pragma unroll
+      for (int pr = 0; pr < 4; ++pr) pair_body(pr, std::true_type{});
+    } else {
+#pragma unroll 1
+      for (int pr = 0; pr < 4; ++pr) pair_body(pr, std::false_type{});
+    }
 
     const bool seg_last = (step == p.k_steps - 1) || (it == n_units - 1);
     if (seg_last) {
       const bool whole = (seg_first_step == 0) && (step == p.k_steps - 1);
-      const int n_base = tile * kTileN + 32 * warp + 2 * g;
-      auto store_c = [&](float (&v)[MG][2][4]) {
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int n = n_base + 16 * c;
-          if (n < p.n) {   // N is a multiple of 16 and n is even: n + 1 is inside too
-            const float b0 = bias != nullptr ? to_f32<T>(bias[n]) : 0.f;
-            const float b1 = bias != nullptr ? to_f32<T>(bias[n + 1]) : 0.f;
-#pragma unroll
-            for (int t = 0; t < MG; ++t) {
-              const int tok = 8 * t + 2 * s;
-              // d0 (n, tok) d1 (n, tok+1) d2 (n+1, tok) d3 (n+1, tok+1)
-              if (tok < p.m)
-                *reinterpret_cast<uint32_t*>(cmat + static_cast<size_t>(tok) * p.n + n) =
-                    P16::make(v[t][c][0] + b0, v[t][c][2] + b1);
-              if (tok + 1 < p.m)
-                *reinterpret_cast<uint32_t*>(cmat + static_cast<size_t>(tok + 1) * p.n + n) =
-                    P16::make(v[t][c][1] + b0, v[t][c][3] + b1);
-            }
-          }
-        }
-      };
       if (whole) {
-        store_c(acc);
+        store_c(acc, tile);
       } else {
-        // this CTA's share of the tile: publish it, and find out whether this warp completes the tile
-        const long long tile_u0 = static_cast<long long>(tile) * p.k_steps;
-        const int first_cta = cta_of_unit(units, ctas, tile_u0);
-        const int last_cta = cta_of_unit(units, ctas, tile_u0 + p.k_steps - 1);
-        const int parts = last_cta - first_cta + 1;
+        // this CTA's share of the tile goes to its slot; the arrival is announced after the
+        // main loop, when no copy is in flight any more (a fence here would wait for all of them)
+        const int first_cta = cta_of_unit(units, ctas, static_cast<long long>(tile) * p.k_steps);
         const int part = static_cast<int>(blockIdx.x) - first_cta;
-        constexpr int kSlotFloats = C::kAccRegs * 32;
-        float* tile_slots = p.slots + (static_cast<size_t>(tile) * p.max_parts * kWarps + warp) * kSlotFloats;
-        const size_t part_stride = static_cast<size_t>(kWarps) * kSlotFloats;
-        float* mine = tile_slots + part * part_stride + lane;
+        float* mine = p.slots + ((static_cast<size_t>(tile) * p.max_parts + part) * kWarps + warp) * kSlotFloats + lane;
 #pragma unroll
         for (int t = 0; t < MG; ++t)
 #pragma unroll
           for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int j = 0; j < 4; ++j) __stcg(mine + ((t * 2 + c) * 4 + j) * 32, acc[t][c][j]);
-        __threadfence();
-        __syncwarp();
-        unsigned int prev = 0u;
-        if (lane == 0) prev = atomicAdd(p.counters + tile * kWarps + warp, 1u);
-        prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
-        if (prev == static_cast<unsigned int>(parts - 1)) {
-          if (lane == 0) p.counters[tile * kWarps + warp] = 0u;   // ready for the next launch
-          __threadfence();
-          float sum[MG][2][4];
-#pragma unroll
-          for (int t = 0; t < MG; ++t)
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-#pragma unroll
-              for (int j = 0; j < 4; ++j) sum[t][c][j] = 0.f;
-          for (int qd = 0; qd < parts; ++qd) {
-            const float* src = tile_slots + qd * part_stride + lane;
-#pragma unroll
-            for (int t = 0; t < MG; ++t)
-#pragma unroll
-              for (int c = 0; c < 2; ++c)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) sum[t][c][j] += __ldcg(src + ((t * 2 + c) * 4 + j) * 32);
-          }
-          store_c(sum);
-        }
+        if (n_pub == 0) pub_tile[0] = tile; else pub_tile[1] = tile;
+        ++n_pub;
       }
 #pragma unroll
       for (int t = 0; t < MG; ++t)
@@ -421,6 +424,44 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_decode_kernel(const Params 
     if (seg_last) seg_first_step = step;
   }
   cp_async_wait<0>();
+
+  // ------------------------------ split tiles ------------------------------
+  // Announce this warp's partials; the warp that completes a (tile, warp) count adds the
+  // parts in part order and writes C.
+  if (n_pub > 0) {
+    __threadfence();
+    __syncwarp();
+#pragma unroll 1
+    for (int r = 0; r < n_pub; ++r) {
+      const int tl = r == 0 ? pub_tile[0] : pub_tile[1];
+      const long long tile_u0 = static_cast<long long>(tl) * p.k_steps;
+      const int first_cta = cta_of_unit(units, ctas, tile_u0);
+      const int parts = cta_of_unit(units, ctas, tile_u0 + p.k_steps - 1) - first_cta + 1;
+      unsigned int prev = 0u;
+      if (lane == 0) prev = atomicAdd(p.counters + tl * kWarps + warp, 1u);
+      prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
+      if (prev != static_cast<unsigned int>(parts - 1)) continue;
+      if (lane == 0) p.counters[tl * kWarps + warp] = 0u;   // ready for the next launch
+      __threadfence();
+      const float* tile_slots = p.slots + (static_cast<size_t>(tl) * p.max_parts * kWarps + warp) * kSlotFloats + lane;
+#pragma unroll
+      for (int t = 0; t < MG; ++t)
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[t][c][j] = 0.f;
+      for (int qd = 0; qd < parts; ++qd) {
+        const float* src = tile_slots + qd * part_stride;
+#pragma unroll
+        for (int t = 0; t < MG; ++t)
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[t][c][j] += __ldcg(src + ((t * 2 + c) * 4 + j) * 32);
+      }
+      store_c(acc, tl);
+    }
+  }
 }
 
 template <typename T, int MG>
@@ -435,6 +476,9 @@ ks_status_t launch_t(const Params& p, int grid, cudaStream_t stream) {
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+      if (e != cudaSuccess) return cuda_status(e, "ks_gemm_w4a16");
+      // all of the SM's unified storage as shared memory, or the second CTA does not fit
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
       if (e != cudaSuccess) return cuda_status(e, "ks_gemm_w4a16");
       attr_done[dev] = true;
     }
@@ -474,8 +518,8 @@ Geometry geometry_of(const W4A16Args& a) {
   g.n_tiles = static_cast<int>((a.n + kTileN - 1) / kTileN);
   g.k_steps = static_cast<int>(a.k / kStepK);
   const long long units = static_cast<long long>(g.n_tiles) * g.k_steps;
-  const int sms = sm_count();
-  g.grid = static_cast<int>(units < sms ? units : sms);
+  const int ctas = sm_count() * (g.mg <= 4 ? 2 : 1);
+  g.grid = static_cast<int>(units < ctas ? units : ctas);
   const long long per_cta = units / g.grid;   // shortest run
   g.max_parts = static_cast<int>((g.k_steps + per_cta - 1) / per_cta) + 1;
   g.slot_bytes = static_cast<size_t>(g.n_tiles) * g.max_parts * kWarps * (g.mg * 8 * 32) * sizeof(float);

@@ -1,6 +1,8 @@
-"""Out-parameter wrappers of the grouped GEMMs; ``grouped_gemm`` has the
-signature of ``bindings/python/kernel_set/moe.py:189-217`` of the reference
-project, ``grouped_gemm_fp8_blockwise`` wraps the added block-scaled symbol."""
+"""Out-parameter wrappers of the mixture-of-experts entry points with the
+signatures of ``bindings/python/kernel_set/moe.py`` of the reference project
+(``gate_softmax_topk`` :42-71, ``compute_permutation`` :109-134, ``permute``
+:137-159, ``unpermute`` :162-186, ``grouped_gemm`` :189-217);
+``grouped_gemm_fp8_blockwise`` and ``permute_quant_fp8`` wrap added symbols."""
 from __future__ import annotations
 
 from typing import Optional
@@ -46,4 +48,69 @@ def grouped_gemm_fp8_blockwise(out: TensorLike, a_fp8: TensorLike, b_fp8: Tensor
         i32_ptr(expert_offsets, name="expert_offsets"), int(num_experts), int(total_rows), int(n), int(k),
         int(block_n), int(block_k), 1 if b_layout == "nk" else 0, int(fp8_dtype), int(out_dtype),
         default_stream(stream, a_fp8)), "ks_moe_grouped_gemm_fp8_blockwise")
+    return out
+
+
+def gate_softmax_topk(out_weights: TensorLike, out_indices: TensorLike, logits: TensorLike, num_tokens: int,
+                      num_experts: int, top_k: int, renormalize: bool = True, dtype: Optional[int] = None,
+                      stream: TensorLike = None):
+    """Softmax over experts then top-k. ``logits [num_tokens, num_experts]``;
+    ``out_weights [num_tokens, top_k]`` fp32; ``out_indices [num_tokens, top_k]``
+    int32. Returns ``(out_weights, out_indices)``."""
+    dt = infer_dtype(logits, dtype)
+    check(lib.ks_moe_gate_softmax_topk(f32_ptr(out_weights, name="out_weights"),
+                                       i32_ptr(out_indices, name="out_indices"), ptr(logits, name="logits"),
+                                       int(num_tokens), int(num_experts), int(top_k), 1 if renormalize else 0, dt,
+                                       default_stream(stream, logits)), "ks_moe_gate_softmax_topk")
+    return out_weights, out_indices
+
+
+def compute_permutation(sorted_token_ids: TensorLike, expert_offsets: TensorLike, topk_indices: TensorLike,
+                        num_tokens: int, num_experts: int, top_k: int, stream: TensorLike = None):
+    """The permutation that groups (token, slot) pairs by expert.
+    ``topk_indices [num_tokens, top_k]`` int32; ``sorted_token_ids
+    [num_tokens*top_k]`` int32; ``expert_offsets [num_experts+1]`` int32.
+    Returns ``(sorted_token_ids, expert_offsets)``."""
+    check(lib.ks_moe_compute_permutation(i32_ptr(sorted_token_ids, name="sorted_token_ids"),
+                                         i32_ptr(expert_offsets, name="expert_offsets"),
+                                         i32_ptr(topk_indices, name="topk_indices"), int(num_tokens),
+                                         int(num_experts), int(top_k), default_stream(stream, topk_indices)),
+          "ks_moe_compute_permutation")
+    return sorted_token_ids, expert_offsets
+
+
+def permute(permuted: TensorLike, input: TensorLike, sorted_token_ids: TensorLike, num_tokens: int, top_k: int,
+            hidden: int, dtype: Optional[int] = None, stream: TensorLike = None) -> TensorLike:
+    """Gather rows of ``input [num_tokens, hidden]`` into ``permuted
+    [num_tokens*top_k, hidden]`` following ``sorted_token_ids``."""
+    dt = infer_dtype(input, dtype)
+    check(lib.ks_moe_permute(ptr(permuted, name="permuted"), ptr(input, name="input"),
+                             i32_ptr(sorted_token_ids, name="sorted_token_ids"), int(num_tokens), int(top_k),
+                             int(hidden), dt, default_stream(stream, input)), "ks_moe_permute")
+    return permuted
+
+
+def permute_quant_fp8(out_fp8: TensorLike, out_scale: TensorLike, input: TensorLike, sorted_token_ids: TensorLike,
+                      num_tokens: int, top_k: int, hidden: int, in_dtype: Optional[int] = None,
+                      fp8_dtype: Optional[int] = None, stream: TensorLike = None):
+    """``permute`` fused with the 1 x 128 FP8 quantizer. Returns ``(out_fp8, out_scale)``."""
+    dt = infer_dtype(input, in_dtype)
+    if fp8_dtype is None:
+        fp8_dtype = infer_dtype(out_fp8, None)
+    check(lib.ks_moe_permute_quant_fp8(ptr(out_fp8, name="out_fp8"), f32_ptr(out_scale, name="out_scale"),
+                                       ptr(input, name="input"), i32_ptr(sorted_token_ids, name="sorted_token_ids"),
+                                       int(num_tokens), int(top_k), int(hidden), dt, int(fp8_dtype),
+                                       default_stream(stream, input)), "ks_moe_permute_quant_fp8")
+    return out_fp8, out_scale
+
+
+def unpermute(out: TensorLike, permuted: TensorLike, sorted_token_ids: TensorLike, routing_weights: TensorLike,
+              num_tokens: int, top_k: int, hidden: int, dtype: Optional[int] = None,
+              stream: TensorLike = None) -> TensorLike:
+    """``out[token] = sum_k weight[token,k] * permuted[pos(token,k)]``."""
+    dt = infer_dtype(permuted, dtype)
+    check(lib.ks_moe_unpermute(ptr(out, name="out"), ptr(permuted, name="permuted"),
+                               i32_ptr(sorted_token_ids, name="sorted_token_ids"),
+                               f32_ptr(routing_weights, name="routing_weights"), int(num_tokens), int(top_k),
+                               int(hidden), dt, default_stream(stream, permuted)), "ks_moe_unpermute")
     return out

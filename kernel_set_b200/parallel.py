@@ -73,20 +73,6 @@ def expert_range(num_experts: int, rank: int, world: int) -> Tuple[int, int]:
     return min(rank * per, num_experts), min((rank + 1) * per, num_experts)
 
 
-def plan_dispatch(expert_ids: torch.Tensor, num_experts: int, world: int):
-    """For this rank's (token, slot) pairs: the order that sorts them by expert
-    (stable), and how many go to each rank. ``expert_ids`` is [T, k]."""
-    flat = expert_ids.reshape(-1).to(torch.int64)
-    order = torch.sort(flat, stable=True).indices
-    counts = torch.bincount(flat, minlength=num_experts)
-    per = -(-num_experts // world)
-    pad = per * world - num_experts
-    if pad:
-        counts = torch.cat([counts, counts.new_zeros(pad)])
-    send_counts = counts.view(world, per).sum(1)
-    return order, counts[:num_experts], send_counts
-
-
 def exchange_counts(per_expert_counts: torch.Tensor, num_experts: int, world: int, group=None) -> torch.Tensor:
     """All ranks' per-expert counts for the experts this rank owns:
     returns [world, experts_per_rank] (row r = what rank r sends here)."""
@@ -108,26 +94,23 @@ def all_to_all_rows(rows: torch.Tensor, send_counts: Sequence[int], recv_counts:
     return out
 
 
-def received_to_expert_major(recv_counts_matrix: torch.Tensor):
+def received_to_expert_major(recv_counts_matrix: torch.Tensor, total: int):
     """Rows arrive grouped by source rank, and inside a source by local expert.
-    Returns (perm, offsets): ``received[perm]`` is sorted by local expert (source
-    rank order inside an expert), ``offsets`` int32 [E_local+1]."""
+    Returns (perm, offsets) on the matrix's device, computed without a host read:
+    ``received[perm]`` is sorted by local expert (source-rank order inside an
+    expert), ``offsets`` int32 [E_local+1]. ``total`` is the number of rows."""
     world, per = recv_counts_matrix.shape
-    counts = recv_counts_matrix.to(torch.int64)
-    src_base = torch.zeros(world, per, dtype=torch.int64)
-    flat = counts.reshape(-1)
-    starts = torch.cumsum(flat, 0) - flat
-    src_base = starts.view(world, per)
-    idx: List[torch.Tensor] = []
-    for e in range(per):
-        for r in range(world):
-            c = int(counts[r, e])
-            if c:
-                idx.append(torch.arange(c, dtype=torch.int64) + int(src_base[r, e]))
-    perm = torch.cat(idx) if idx else torch.zeros(0, dtype=torch.int64)
-    offsets = torch.zeros(per + 1, dtype=torch.int32)
-    offsets[1:] = torch.cumsum(counts.sum(0), 0).to(torch.int32)
-    return perm, offsets
+    dev = recv_counts_matrix.device
+    c = recv_counts_matrix.to(torch.int64)
+    flat = c.reshape(-1)                                            # source-major: how the rows lie
+    src_start_em = (torch.cumsum(flat, 0) - flat).view(world, per).t().contiguous().reshape(-1)
+    c_em = c.t().contiguous().reshape(-1)                           # expert-major: how they should lie
+    dst_start_em = torch.cumsum(c_em, 0) - c_em
+    block = torch.repeat_interleave(torch.arange(per * world, device=dev), c_em, output_size=int(total))
+    perm = src_start_em[block] + (torch.arange(int(total), device=dev) - dst_start_em[block])
+    offsets = torch.zeros(per + 1, dtype=torch.int32, device=dev)
+    offsets[1:] = torch.cumsum(c.sum(0), 0).to(torch.int32)
+    return perm.to(torch.int32), offsets
 
 
 # ------------------------------------------------------------------------------
@@ -135,8 +118,14 @@ def received_to_expert_major(recv_counts_matrix: torch.Tensor):
 #   ops.quant(x, group_size) -> (codes, scales)
 #   ops.fp8_gemm(a8, b8, a_scale, b_scale, b_layout, out_dtype) -> out
 #   ops.grouped_fp8_gemm(a8, b8, expert_offsets, a_scale, b_scale, n, k, b_layout) -> out
-# The default is this library (CUDA tensors). Anything with the same three
-# methods can stand in, which is how the CPU tests drive the sharding logic.
+#   ops.permutation(topk_ids int32 [T,k], num_experts) -> (sorted_token_ids, expert_offsets)
+#   ops.permute_quant(x, sorted_token_ids, top_k) -> (codes, scales) of the gathered rows
+#   ops.gather_rows(x, index int32) -> x[index]
+#   ops.swiglu_quant(gate_up) -> (codes, scales) of silu(gate) * up
+#   ops.unpermute(y, sorted_token_ids, weights, num_tokens, top_k) -> weighted sum per token
+# The default is this library (CUDA tensors, every step a kernel on the current
+# stream, no host round trip). Anything with the same methods can stand in,
+# which is how the CPU tests drive the sharding logic.
 # ------------------------------------------------------------------------------
 class LibraryOps:
     """The CUDA library as the per-device backend of the sharded operators."""
@@ -152,6 +141,39 @@ class LibraryOps:
     def grouped_fp8_gemm(self, a8, b8, expert_offsets, a_scale, b_scale, n, k, b_layout="nk"):
         from . import dispatch
         return dispatch.moe(a8, b8, expert_offsets, n=n, k=k, a_scale=a_scale, b_scale=b_scale, b_layout=b_layout)
+
+    def permutation(self, topk_ids, num_experts):
+        from . import moe
+        t, k = topk_ids.shape
+        sorted_ids = torch.empty(t * k, dtype=torch.int32, device=topk_ids.device)
+        offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=topk_ids.device)
+        return moe.compute_permutation(sorted_ids, offsets, topk_ids, t, num_experts, k)
+
+    def permute_quant(self, x, sorted_ids, top_k):
+        from . import moe
+        t, hidden = x.shape
+        out = torch.empty(t * top_k, hidden, dtype=torch.float8_e4m3fn, device=x.device)
+        scale = torch.empty(t * top_k, hidden // BLOCK, dtype=torch.float32, device=x.device)
+        return moe.permute_quant_fp8(out, scale, x, sorted_ids, t, top_k, hidden)
+
+    def gather_rows(self, x, index):
+        from . import moe
+        out = torch.empty_like(x)
+        if x.shape[0]:
+            moe.permute(out, x, index, x.shape[0], 1, x.shape[1])
+        return out
+
+    def swiglu_quant(self, gate_up):
+        from . import activation
+        rows, two_inter = gate_up.shape
+        out = torch.empty(rows, two_inter // 2, dtype=torch.float8_e4m3fn, device=gate_up.device)
+        scale = torch.empty(rows, two_inter // 2 // BLOCK, dtype=torch.float32, device=gate_up.device)
+        return activation.swiglu_packed_quant_fp8(out, scale, gate_up, rows, two_inter // 2)
+
+    def unpermute(self, y, sorted_ids, weights, num_tokens, top_k):
+        from . import moe
+        out = torch.empty(num_tokens, y.shape[1], dtype=y.dtype, device=y.device)
+        return moe.unpermute(out, y, sorted_ids, weights, num_tokens, top_k, y.shape[1])
 
 
 def column_parallel_linear(x: torch.Tensor, w8_shard: torch.Tensor, ws_shard: torch.Tensor, ops=None,
@@ -189,49 +211,51 @@ def expert_parallel_moe(tokens: torch.Tensor, topk_ids: torch.Tensor, topk_weigh
     tokens [T_local, H] bf16 (this rank's tokens); topk_ids / topk_weights
     [T_local, k]; w1_8 [E_local, 2I, H] with w1_s [E_local, 2I/128, H/128];
     w2_8 [E_local, H, I] with w2_s [E_local, H/128, I/128] (this rank's experts,
-    weights stored [N,K]). Steps: sort the (token, slot) pairs by expert ->
-    exchange counts -> all-to-all the rows to their expert's rank -> regroup by
-    local expert -> grouped FP8 GEMM (gate/up) -> SwiGLU -> quantize -> grouped
-    FP8 GEMM (down) -> all-to-all back -> weighted sum per token.
+    weights stored [N,K]). Steps, each one kernel (or one collective) on the
+    tensors' device: counting-sort permutation of the (token, slot) pairs by
+    expert -> gather fused with the 1 x 128 quantizer (rows travel as fp8 codes
+    plus fp32 scales, half the bytes of bf16) -> exchange counts -> all-to-all
+    to the experts' ranks -> regroup by local expert -> grouped FP8 GEMM
+    (gate/up) -> SwiGLU fused with the re-quantisation -> grouped FP8 GEMM
+    (down) -> all-to-all back -> weighted sum per token in pair order.
+    With more than one rank the split sizes of the all-to-alls are read back to
+    the host once (two small vectors); with one rank nothing leaves the device.
     Returns [T_local, H] bf16."""
     ops = ops or LibraryOps()
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     t_local, hidden = tokens.shape
     k = topk_ids.shape[1]
     dev = tokens.device
-    order, per_expert, send_counts = plan_dispatch(topk_ids.cpu(), num_experts, world)
-    rows = tokens.repeat_interleave(k, dim=0)[order.to(dev)]          # (token, slot) pairs sorted by expert
-    if world > 1:
-        recv_matrix = exchange_counts(per_expert.to(dev), num_experts, world, group).cpu()
-        recv_counts = recv_matrix.sum(1)
-        received = all_to_all_rows(rows, send_counts.tolist(), recv_counts.tolist(), group)
-    else:
-        per = -(-num_experts // world)
-        recv_matrix = per_expert.view(1, per)
-        recv_counts = recv_matrix.sum(1)
-        received = rows
-    perm, offsets = received_to_expert_major(recv_matrix)
-    x = received[perm.to(dev)]
-    offs_dev = offsets.to(dev)
-    e_local = w1_8.shape[0]
+    ids32 = topk_ids.to(device=dev, dtype=torch.int32).contiguous()
+    weights = topk_weights.to(device=dev, dtype=torch.float32).contiguous()
+    sorted_ids, offsets = ops.permutation(ids32, num_experts)      # sorted by expert = by destination rank
+    x8, x_s = ops.permute_quant(tokens, sorted_ids, k)
     inter2, inter = w1_8.shape[1], w2_8.shape[2]
-    if x.shape[0] > 0:
-        x8, x_s = ops.quant(x, BLOCK)
-        h = ops.grouped_fp8_gemm(x8, w1_8, offs_dev, x_s, w1_s, inter2, hidden, "nk")
-        act = swiglu(h)
-        a8, a_s = ops.quant(act, BLOCK)
-        y = ops.grouped_fp8_gemm(a8, w2_8, offs_dev, a_s, w2_s, hidden, inter, "nk")
-    else:
-        y = x.new_zeros((0, hidden))
-    assert e_local * 1 >= 0
-    # undo the regrouping, send every row back to the rank its token lives on
-    back = torch.empty_like(y)
-    back[perm.to(dev)] = y
     if world > 1:
-        returned = all_to_all_rows(back, recv_counts.tolist(), send_counts.tolist(), group)
+        per = -(-num_experts // world)
+        counts = (offsets[1:] - offsets[:-1]).to(torch.int64)
+        recv_matrix = exchange_counts(counts, num_experts, world, group)
+        pad = per * world - num_experts
+        padded = torch.cat([counts, counts.new_zeros(pad)]) if pad else counts
+        sizes = torch.stack([padded.view(world, per).sum(1), recv_matrix.sum(1)]).cpu()   # the one host read
+        send_l, recv_l = sizes[0].tolist(), sizes[1].tolist()
+        r8 = all_to_all_rows(x8.view(torch.uint8), send_l, recv_l, group).view(x8.dtype)
+        r_s = all_to_all_rows(x_s, send_l, recv_l, group)
+        perm, local_offsets = received_to_expert_major(recv_matrix, sum(recv_l))
+        r8 = ops.gather_rows(r8, perm)
+        r_s = ops.gather_rows(r_s, perm)
     else:
-        returned = back
-    unsorted = torch.empty_like(returned)
-    unsorted[order.to(dev)] = returned
-    out = (unsorted.view(t_local, k, hidden).float() * topk_weights.to(dev).float().unsqueeze(-1)).sum(1)
-    return out.to(tokens.dtype)
+        r8, r_s, local_offsets = x8, x_s, offsets
+    if r8.shape[0] > 0:
+        h = ops.grouped_fp8_gemm(r8, w1_8, local_offsets, r_s, w1_s, inter2, hidden, "nk")
+        a8, a_s = ops.swiglu_quant(h)
+        y = ops.grouped_fp8_gemm(a8, w2_8, local_offsets, a_s, w2_s, hidden, inter, "nk")
+    else:
+        y = tokens.new_zeros((0, hidden))
+    if world > 1:
+        # undo the regrouping (the inverse of a permutation, on the device), then send every
+        # row back to the rank its token lives on
+        inverse = torch.empty_like(perm)
+        inverse[perm.to(torch.int64)] = torch.arange(perm.numel(), dtype=perm.dtype, device=perm.device)
+        y = all_to_all_rows(ops.gather_rows(y, inverse), recv_l, send_l, group)
+    return ops.unpermute(y, sorted_ids, weights, t_local, k)

@@ -2,8 +2,8 @@
 on-device checker: ``oracle/_ref/libkernel_set_ref.so``. TEST INFRASTRUCTURE.
 
 The sources are compiled where they lie in a checkout of the reference project
-(environment variable ``KS_REFERENCE_ROOT``, with the build container's checkout as the
-default); nothing is copied. The result
+(environment variable ``KS_REFERENCE_ROOT``, else a checkout named ``reference`` beside this
+repository); nothing is copied. The result
 is git-ignored. When the checkout is absent (a machine that only received the
 prebuilt file) the function reports that and returns ``None``.
 
@@ -35,7 +35,11 @@ SOURCES = [
 
 
 def build_ref(verbose: bool = False):
-    root = os.environ.get("KS_REFERENCE_ROOT", "/root/reference")
+    root = os.environ.get("KS_REFERENCE_ROOT")
+    if not root:
+        # a checkout named `reference` beside this repository, if there is one
+        beside = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+        root = beside if os.path.isdir(beside) else ""
     if not os.path.isdir(os.path.join(root, "kernels", "src")):
         return OUT if os.path.exists(OUT) else None
     srcs = [os.path.join(root, s) for s in SOURCES]

@@ -251,6 +251,41 @@ def sort_by_expert(expert_ids: torch.Tensor, num_experts: int):
     return order, offsets
 
 
+def moe_permute(x: torch.Tensor, sorted_token_ids: torch.Tensor, top_k: int) -> torch.Tensor:
+    """Gather rows by the permutation: row r of the result is token
+    ``sorted_token_ids[r] // top_k`` (bench.py:2546-2548)."""
+    return x.index_select(0, sorted_token_ids.to(torch.int64) // top_k)
+
+
+def moe_unpermute(permuted: torch.Tensor, sorted_token_ids: torch.Tensor, weights: torch.Tensor, num_tokens: int,
+                  top_k: int, out_dtype="same") -> torch.Tensor:
+    """``out[token] = sum_k weight[token,k] * permuted[pos(token,k)]`` as a weighted
+    scatter-add in fp32 (bench.py:2570-2579). ``out_dtype=None`` returns fp32."""
+    ids = sorted_token_ids.to(torch.int64)
+    dst_tok, slot = ids // top_k, ids % top_k
+    contrib = permuted.float() * weights[dst_tok, slot].unsqueeze(1).float()
+    ref = torch.zeros(num_tokens, permuted.shape[1], dtype=torch.float32)
+    ref.index_add_(0, dst_tok, contrib)
+    if out_dtype is None:
+        return ref
+    return ref.to(permuted.dtype if out_dtype == "same" else out_dtype)
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor, out_dtype="same") -> torch.Tensor:
+    """``silu(gate.float()) * up.float()`` rounded once (bench.py:957-958)."""
+    ref = torch.nn.functional.silu(gate.float()) * up.float()
+    if out_dtype is None:
+        return ref
+    return ref.to(gate.dtype if out_dtype == "same" else out_dtype)
+
+
+def swiglu_packed(x: torch.Tensor, out_dtype="same") -> torch.Tensor:
+    """Packed form: gate = x[:, :inter], up = x[:, inter:]
+    (kernels/src/activation/gated_mlp.cu:91-117)."""
+    inter = x.shape[1] // 2
+    return swiglu(x[:, :inter], x[:, inter:], out_dtype)
+
+
 # --------------------------------------------------------------------------- #
 # error measures
 # --------------------------------------------------------------------------- #

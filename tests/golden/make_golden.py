@@ -11,7 +11,8 @@ How the reference is made to run without a GPU:
   * ``benchmarks/bench.py::_make_fp8_blockwise_inputs`` is called as is: its
     outputs (fp8 codes, scales, dequantized operands) are reference data;
   * for the ops whose torch statement is written inline in a bench function
-    (w4a16, int4 dequant, grouped GEMM), that function is executed with the
+    (w4a16, int4 dequant, grouped GEMM, the MoE gate / permute / unpermute
+    steps, SwiGLU), that function is executed with the
     oracle standing in for the library call. The function then compares the
     stand-in's output with its own inline torch reference and reports
     ``rel_err``; the script insists on exactly 0.0, which proves the oracle
@@ -30,7 +31,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("KS_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("KS_REFERENCE_ROOT")
+if not REF:
+    raise SystemExit("set KS_REFERENCE_ROOT to a checkout of the reference project")
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "oracle"))
 import ks_oracle as orc  # noqa: E402
@@ -141,6 +144,81 @@ def main():
     assert r.rel_err == 0.0, (r.rel_err, r.status)
     np.savez_compressed(os.path.join(HERE, "grouped_gemm_bf16.npz"), **record["grouped"])
     print("moe_grouped_gemm reference bench rel_err", r.rel_err)
+
+    # ---- MoE steps around the grouped GEMM, and SwiGLU ----
+    def fake_gate(weights, indices, logits, num_tokens, E, k, renormalize=True, **kw):
+        w, i = orc.moe_route(logits, k)
+        weights.copy_(w)
+        indices.copy_(i.to(torch.int32))
+        record["gate"] = dict(logits=bits16(logits), weights=weights.numpy().copy(), indices=indices.numpy().copy())
+        return weights, indices
+
+    def fake_permutation(sorted_ids, offsets, indices, tokens, E, k, **kw):
+        order, off = orc.sort_by_expert(indices.to(torch.int64), E)
+        sorted_ids.copy_(order.to(torch.int32))
+        offsets.copy_(off)
+        record["perm"] = dict(indices=indices.numpy().copy(), sorted_ids=sorted_ids.numpy().copy(),
+                              offsets=offsets.numpy().copy())
+        return sorted_ids, offsets
+
+    def fake_permute(permuted, x, sorted_ids, tokens, k, hidden, **kw):
+        permuted.copy_(orc.moe_permute(x, sorted_ids, k))
+        record["permute"] = dict(x=bits16(x), sorted_ids=sorted_ids.numpy().copy(), top_k=np.int64(k),
+                                 out=bits16(permuted))
+        return permuted
+
+    def fake_unpermute(out, permuted, sorted_ids, weights, tokens, k, hidden, **kw):
+        out.copy_(orc.moe_unpermute(permuted, sorted_ids, weights, tokens, k))
+        record["unpermute"] = dict(permuted=bits16(permuted), sorted_ids=sorted_ids.numpy().copy(),
+                                   weights=weights.numpy().copy(), top_k=np.int64(k), out=bits16(out))
+        return out
+
+    def fake_swiglu(out, gate, up, **kw):
+        out.copy_(orc.swiglu(gate, up))
+        record["swiglu"] = dict(gate=bits16(gate), up=bits16(up), out=bits16(out))
+        return out
+
+    ks.moe.gate_softmax_topk = fake_gate
+    ks.moe.compute_permutation = fake_permutation
+    ks.moe.permute = fake_permute
+    ks.moe.unpermute = fake_unpermute
+    ks.activation.swiglu = fake_swiglu
+
+    torch.manual_seed(9)
+    r = rb._bench_moe_gate(ctx, 48, 0, 0, 16, 4)
+    assert r.rel_err == 0.0, (r.rel_err, r.status)
+    print("moe_gate reference bench rel_err", r.rel_err)
+    torch.manual_seed(10)
+    r = rb._bench_moe_permute(ctx, 40, 96, 8, 2)
+    assert r.rel_err == 0.0, (r.rel_err, r.status)
+    print("moe_permute reference bench rel_err", r.rel_err)
+    torch.manual_seed(11)
+    r = rb._bench_moe_unpermute(ctx, 40, 96, 8, 2)
+    assert r.rel_err == 0.0, (r.rel_err, r.status)
+    print("moe_unpermute reference bench rel_err", r.rel_err)
+    torch.manual_seed(12)
+    r = rb._bench_swiglu(ctx, 24, 160)
+    assert r.rel_err == 0.0, (r.rel_err, r.status)
+    print("swiglu reference bench rel_err", r.rel_err)
+    flat = {f"{op}.{k}": v for op in ("gate", "perm", "permute", "unpermute", "swiglu") for k, v in record[op].items()}
+    np.savez_compressed(os.path.join(HERE, "moe_steps_bf16.npz"), **flat)
+
+    abi_symbols()
+
+
+def abi_symbols():
+    """Every function the reference's headers declare, as `<header> <symbol>` lines."""
+    import glob
+    import re
+    rows = []
+    for h in sorted(glob.glob(os.path.join(REF, "include", "kernel_set", "*.h"))):
+        text = re.sub(r"/\*.*?\*/", "", open(h).read(), flags=re.S)
+        rows += [(os.path.basename(h), n) for n in re.findall(r"KS_API[^;(]*?\b(ks_[a-z0-9_]+)\s*\(", text)]
+    with open(os.path.join(HERE, "reference_abi_symbols.txt"), "w") as f:
+        f.write("# Every function the reference project's headers declare (include/kernel_set/*.h), one per line:\n"
+                "# <header> <symbol>. Written by tests/golden/make_golden.py (abi_symbols).\n")
+        f.writelines(f"{h} {n}\n" for h, n in rows)
+    print("reference ABI:", len(rows), "functions")
 
 
 if __name__ == "__main__":

@@ -33,12 +33,30 @@ def test_headers_compile_as_c_and_cpp(tmp_path):
 
 def test_every_declared_symbol_is_exported(ks):
     decl = declared_symbols()
-    assert len(decl) == 26, decl
+    assert len(decl) == 34, decl
     out = subprocess.run(["nm", "-D", "--defined-only", ks.LIB_PATH], capture_output=True, text=True, check=True)
     exported = sorted(l.split()[-1] for l in out.stdout.splitlines() if " T " in l)
     assert [s for s in decl if s not in exported] == []
     assert [s for s in exported if not s.startswith("ks_")] == [], "non-ABI symbols leak from the library"
     assert ks._lib._MISSING == []
+
+
+def test_every_reference_symbol_resolves(ks):
+    """Bindings that resolve all of the reference's 89 functions when they load (cgo, a Rust
+    build script) must link: what this library does not implement answers NOT_IMPLEMENTED."""
+    rows = [l.split() for l in open(os.path.join(ROOT, "tests", "golden", "reference_abi_symbols.txt"))
+            if l.strip() and not l.startswith("#")]
+    assert len(rows) == 89
+    ours = set(declared_symbols())
+    for header, name in rows:
+        fn = getattr(ks._lib.lib, name)          # AttributeError = would not link
+        if name not in ours:
+            fn.restype = ctypes.c_int
+            fn.argtypes = []
+            assert fn() == ks.Status.NOT_IMPLEMENTED, name
+            assert name in ks.runtime.last_error_string()
+    implemented = sorted(n for _, n in rows if n in ours)
+    assert len(implemented) == 29 and "ks_moe_unpermute" in implemented and "ks_swiglu_packed" in implemented
 
 
 def test_introspection(ks):
@@ -127,6 +145,25 @@ def test_argument_validation_codes(ks):
         == S.SUCCESS
     assert gf(ONE, ONE, ONE, f32p(ONE), f32p(ONE), i32p(ONE), 2, 8, 8, 8, 128, 128, 5, D.F8E4M3, D.BF16, None) \
         == S.INVALID_ARGUMENT
+    # MoE steps (reference moe_gate.cu / moe_permute.cu launchers) and SwiGLU
+    assert L.ks_moe_gate_softmax_topk(f32p(ONE), i32p(ONE), None, 4, 8, 2, 1, D.BF16, None) == S.INVALID_ARGUMENT
+    assert L.ks_moe_gate_softmax_topk(f32p(ONE), i32p(ONE), ONE, 4, 8, 9, 1, D.BF16, None) == S.INVALID_ARGUMENT
+    assert L.ks_moe_gate_softmax_topk(f32p(ONE), i32p(ONE), ONE, 4, 2000, 2, 1, D.BF16, None) == S.UNSUPPORTED_SHAPE
+    assert L.ks_moe_gate_softmax_topk(f32p(ONE), i32p(ONE), ONE, 4, 8, 2, 1, D.I8, None) == S.UNSUPPORTED_DTYPE
+    assert L.ks_moe_gate_softmax_topk(f32p(ONE), i32p(ONE), ONE, 0, 8, 2, 1, D.BF16, None) == S.SUCCESS
+    assert L.ks_moe_compute_permutation(i32p(ONE), i32p(ONE), i32p(None), 4, 8, 2, None) == S.INVALID_ARGUMENT
+    assert L.ks_moe_compute_permutation(i32p(ONE), i32p(ONE), i32p(ONE), 2 ** 31, 8, 2, None) == S.UNSUPPORTED_SHAPE
+    assert L.ks_moe_permute(ONE, ONE, i32p(ONE), 4, 0, 8, D.BF16, None) == S.INVALID_ARGUMENT
+    assert L.ks_moe_permute(ONE, ONE, i32p(ONE), 4, 2, 8, D.I32, None) == S.UNSUPPORTED_DTYPE
+    assert L.ks_moe_permute(ONE, ONE, i32p(ONE), 0, 2, 8, D.BF16, None) == S.SUCCESS
+    assert L.ks_moe_permute_quant_fp8(ONE, f32p(ONE), ONE, i32p(ONE), 4, 2, 100, D.BF16, D.F8E4M3, None) \
+        == S.UNSUPPORTED_SHAPE
+    assert L.ks_moe_unpermute(ONE, ONE, i32p(ONE), f32p(None), 4, 2, 8, D.BF16, None) == S.INVALID_ARGUMENT
+    assert L.ks_moe_unpermute(ONE, ONE, i32p(ONE), f32p(ONE), 4, 2, 8, D.F8E4M3, None) == S.UNSUPPORTED_DTYPE
+    assert L.ks_swiglu_packed(ONE, None, 4, 8, D.BF16, None) == S.INVALID_ARGUMENT
+    assert L.ks_swiglu(ONE, ONE, ONE, 4, 0, D.BF16, None) == S.INVALID_ARGUMENT
+    assert L.ks_swiglu(ONE, ONE, ONE, 4, 8, D.I8, None) == S.UNSUPPORTED_DTYPE
+    assert L.ks_swiglu_packed_quant_fp8(ONE, f32p(ONE), ONE, 4, 100, D.BF16, D.F8E4M3, None) == S.UNSUPPORTED_SHAPE
     # runtime
     assert L.ks_device_count(None) == S.INVALID_ARGUMENT
     assert L.ks_memcpy(None, ONE, 4, 0, None) == S.INVALID_ARGUMENT

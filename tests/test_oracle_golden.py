@@ -56,6 +56,30 @@ def test_grouped_gemm_matches_reference():
     assert torch.equal(out.view(torch.int16), torch.from_numpy(g["out"]))
 
 
+def test_moe_steps_match_reference():
+    g = golden("moe_steps_bf16.npz")
+    bf = torch.bfloat16
+    logits = from_bits16(g["gate.logits"], bf)
+    w, i = orc.moe_route(logits, g["gate.indices"].shape[1])
+    assert torch.equal(w, torch.from_numpy(g["gate.weights"]))
+    assert torch.equal(i.to(torch.int32), torch.from_numpy(g["gate.indices"]))
+    ids = torch.from_numpy(g["perm.indices"])
+    order, offs = orc.sort_by_expert(ids.to(torch.int64), g["perm.offsets"].shape[0] - 1)
+    assert torch.equal(order.to(torch.int32), torch.from_numpy(g["perm.sorted_ids"]))
+    assert torch.equal(offs, torch.from_numpy(g["perm.offsets"]))
+    x = from_bits16(g["permute.x"], bf)
+    out = orc.moe_permute(x, torch.from_numpy(g["permute.sorted_ids"]), int(g["permute.top_k"]))
+    assert torch.equal(out.view(torch.int16), torch.from_numpy(g["permute.out"]))
+    y = from_bits16(g["unpermute.permuted"], bf)
+    k = int(g["unpermute.top_k"])
+    out = orc.moe_unpermute(y, torch.from_numpy(g["unpermute.sorted_ids"]), torch.from_numpy(g["unpermute.weights"]),
+                            y.shape[0] // k, k)
+    assert torch.equal(out.view(torch.int16), torch.from_numpy(g["unpermute.out"]))
+    gate, up = from_bits16(g["swiglu.gate"], bf), from_bits16(g["swiglu.up"], bf)
+    assert torch.equal(orc.swiglu(gate, up).view(torch.int16), torch.from_numpy(g["swiglu.out"]))
+    assert torch.equal(orc.swiglu_packed(torch.cat([gate, up], 1)).view(torch.int16), torch.from_numpy(g["swiglu.out"]))
+
+
 def test_int4_round_trips():
     gen = torch.Generator().manual_seed(1)
     codes = torch.randint(0, 16, (64, 24), generator=gen).to(torch.int32)

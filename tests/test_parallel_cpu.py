@@ -24,6 +24,24 @@ class OracleOps:
     def grouped_fp8_gemm(self, a8, b8, expert_offsets, a_scale, b_scale, n, k, b_layout="nk"):
         return orc.grouped_gemm_fp8_blockwise(a8, b8, a_scale, b_scale, expert_offsets.tolist(), layout=b_layout)
 
+    def permutation(self, topk_ids, num_experts):
+        order, offsets = orc.sort_by_expert(topk_ids.to(torch.int64), num_experts)
+        return order.to(torch.int32), offsets
+
+    def permute_quant(self, x, sorted_ids, top_k):
+        return orc.quantize_fp8_group(orc.moe_permute(x, sorted_ids, top_k), 128)
+
+    def gather_rows(self, x, index):
+        if x.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+            return x.view(torch.uint8)[index.to(torch.int64)].view(x.dtype)
+        return x[index.to(torch.int64)]
+
+    def swiglu_quant(self, gate_up):
+        return orc.quantize_fp8_group(orc.swiglu_packed(gate_up), 128)
+
+    def unpermute(self, y, sorted_ids, weights, num_tokens, top_k):
+        return orc.moe_unpermute(y, sorted_ids, weights, num_tokens, top_k)
+
 
 def test_block_range_covers_everything_in_whole_blocks():
     for total in (7168, 896, 300, 128, 100):
@@ -155,3 +173,19 @@ def test_gloo_world2_row_parallel_and_expert_parallel():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert sorted(results) == [(0, True, True), (1, True, True)]
+
+
+def test_received_to_expert_major_matches_a_plain_sort():
+    g = torch.Generator().manual_seed(5)
+    for world, per in ((1, 4), (2, 3), (4, 5)):
+        counts = torch.randint(0, 4, (world, per), generator=g)
+        counts[0, 0] = 0
+        total = int(counts.sum())
+        # label every arriving row with its local expert, in arrival order (source-major)
+        labels = torch.cat([torch.full((int(counts[r, e]),), e) for r in range(world) for e in range(per)]) \
+            if total else torch.zeros(0, dtype=torch.int64)
+        perm, offsets = par.received_to_expert_major(counts, total)
+        assert perm.dtype == torch.int32 and offsets.dtype == torch.int32
+        expect = torch.sort(labels, stable=True).indices
+        assert torch.equal(perm.to(torch.int64), expect)
+        assert offsets.tolist() == [0] + torch.cumsum(counts.sum(0), 0).tolist()
