@@ -106,7 +106,6 @@ ks_status_t poll_kernel_fault(const char* where) {
   *static_cast<volatile unsigned int*>(d->fault_host) = 0u;
   // a kernel that stopped half-way may have left split-K arrival counters non-zero
   sm100::stream_scratch_mark_dirty(1);
-  sm100::stream_scratch_mark_dirty(3);
   char buf[160];
   snprintf(buf, sizeof(buf),
            "%s: an earlier kernel on this device gave up on a bounded wait (code 0x%08x)",

@@ -27,14 +27,12 @@
 // Last partial round of a dense problem: when T tiles leave T mod #CTAs tiles for a final
 // round that would keep most SMs idle (896 tiles on 148 SMs: 8 tiles, 140 idle SMs for a
 // whole tile time), those tiles are cut along K into S parts (S <= 8, parts x tiles <=
-// #CTAs). Each part's epilogue warps write their fp32 partial to a slot; per (tile, warp,
-// 32-column slice) a counter finds the last part to arrive, which adds the parts in part
-// order (reproducible) and stores the slice. Parts bump their slices' counters in rotated
-// order, so parts that finish together each end up reducing a different slice; nobody waits.
-// The parts are every CTA's FIRST work item, not its last: all CTAs start together, so the
-// parts of a tile do finish together and the reduction spreads over them (as the last item
-// they arrived one by one and the last one reduced the whole tile alone: 3 % gained instead
-// of 10 %).
+// #CTAs), each a CTA's first work item. A part's epilogue warps write their fp32 partial to
+// a slot; split_reduce_kernel, launched behind the GEMM on the same stream, adds the parts in
+// part order (reproducible) and writes the tiles. (Letting the last part to arrive reduce a
+// tile inside the GEMM kernel measured 3-4 % gain instead of the 10 % the idle round costs:
+// one CTA then reads S x 128 KB behind a fence and four dependent atomics while its tensor
+// core waits.)
 // Measured on B200 (in-kernel cycle counters): a K-block of a 128 x 256 tile takes
 // ~850 cycles against 512 of tensor work. The epilogue's share is a serial chain per
 // warp (barrier test ~100, eight dependent TMEM loads ~55 each, 128 FMAs per thread:
@@ -138,7 +136,6 @@ struct Params {
   int split_items;        // number of K-part items (tail tiles x split_s), at most the grid size
   int split_s;            // 1 = no split
   float4* split_slots;    // [tail tile][part][epilogue warp][16-byte column chunk][lane]
-  unsigned int* split_counters;  // [tail tile][epilogue warp][32-column slice], zero between launches
 };
 
 struct TileCoord {
@@ -442,58 +439,16 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
       bool stored = false;
       if constexpr (!GROUPED) {
         if (ok && tc.part >= 0) {
-          // One K-part of a split tile. The warp's 32 x EC partial goes to its slot (a lane
-          // writes and later reads the same addresses, 16 bytes per column chunk, chunks 512 B
-          // apart: every store and load of the warp is one contiguous 512-byte piece).
+          // One K-part of a split tile. The warp's 32 x EC partial goes to its slot (16 bytes
+          // per lane and column chunk, chunks 512 B apart: every store of the warp is one
+          // contiguous 512-byte piece); split_reduce_kernel adds the parts up afterwards.
           constexpr int kChunks = EC / 4;      // float4 chunks per lane
-          constexpr int kSlices = EC / 32;     // 32-column slices, one counter each
           const int ew = warp - 4;
           const size_t warp_f4 = static_cast<size_t>(kChunks) * 32;
           float4* mine = p.split_slots + ((static_cast<size_t>(tc.tail) * p.split_s + tc.part) * C::kEpiWarps + ew) * warp_f4 + lane;
 #pragma unroll
           for (int c4 = 0; c4 < kChunks; ++c4)
             __stcg(mine + c4 * 32, make_float4(acc[2 * c4].x, acc[2 * c4].y, acc[2 * c4 + 1].x, acc[2 * c4 + 1].y));
-          __threadfence();
-          __syncwarp();
-          unsigned int* ctr = p.split_counters + (static_cast<size_t>(tc.tail) * C::kEpiWarps + ew) * kSlices;
-#pragma unroll 1
-          for (int j = 0; j < kSlices; ++j) {
-            const int sl = (tc.part + j) % kSlices;
-            unsigned int prev = 0u;
-            if (lane == 0) prev = atomicAdd(ctr + sl, 1u);
-            prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
-            if (prev != static_cast<unsigned int>(p.split_s - 1)) continue;
-            // this warp completes the slice: parts are added in part order
-            if (lane == 0) ctr[sl] = 0u;   // ready for the next launch
-            __threadfence();
-            float4 sum[8];
-#pragma unroll
-            for (int c4 = 0; c4 < 8; ++c4) sum[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int q = 0; q < p.split_s; ++q) {
-              const float4* src = p.split_slots + ((static_cast<size_t>(tc.tail) * p.split_s + q) * C::kEpiWarps + ew) * warp_f4 + lane + sl * 8 * 32;
-              float4 v[8];
-#pragma unroll
-              for (int c4 = 0; c4 < 8; ++c4) v[c4] = __ldcg(src + c4 * 32);
-#pragma unroll
-              for (int c4 = 0; c4 < 8; ++c4) {
-                sum[c4].x += v[c4].x; sum[c4].y += v[c4].y; sum[c4].z += v[c4].z; sum[c4].w += v[c4].w;
-              }
-            }
-            if (row_ok) {
-              OutT* dst = out + static_cast<size_t>(row) * p.n + col0 + sl * 32;
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const int valid = p.n - (col0 + sl * 32 + h * 16);
-                float v16[16];
-#pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
-                  v16[4 * c4] = sum[4 * h + c4].x; v16[4 * c4 + 1] = sum[4 * h + c4].y;
-                  v16[4 * c4 + 2] = sum[4 * h + c4].z; v16[4 * c4 + 3] = sum[4 * h + c4].w;
-                }
-                if (valid > 0) store_16<OutT>(dst + h * 16, v16, p.vec_store != 0, valid);
-              }
-            }
-          }
           stored = true;
         }
         if (ok && !stored && p.tma_store) {
@@ -562,6 +517,59 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
   }
 }
 
+// Sum of the K-parts of the split tiles: one thread per (tile, epilogue warp, column chunk,
+// lane) reads its 16 bytes of every part in part order and writes four outputs.
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(256)
+split_reduce_kernel(OutT* __restrict__ out, const float4* __restrict__ slots, int split_from, int split_s, int tails,
+                    int tiles_m, int tiles_n, int m, int n, int vec_ok) {
+  using C = Cfg<BN>;
+  constexpr int EC = C::kEpiCols;
+  constexpr int kChunks = EC / 4;
+  constexpr int kPerTile = C::kEpiWarps * kChunks * 32;   // float4 per (tile, part)
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tails * kPerTile) return;
+  const int tail = idx / kPerTile;
+  const int r = idx - tail * kPerTile;
+  const int ew = r / (kChunks * 32);
+  const int c4 = (r / 32) % kChunks;
+  const int lane = r & 31;
+  // the tile's place in the output: the column-panel order of locate_tile
+  constexpr int kPanel = KSB_FP8_PANEL;
+  const int t = split_from + tail;
+  const int per_panel = kPanel * tiles_m;
+  const int panel = t / per_panel;
+  const int rr = t - panel * per_panel;
+  const int width = (tiles_n - panel * kPanel) < kPanel ? (tiles_n - panel * kPanel) : kPanel;
+  const int mt = rr / width;
+  const int nt = panel * kPanel + (rr - mt * width);
+  const int row = mt * kBM + (ew & 3) * 32 + lane;
+  const int col = nt * BN + (ew >> 2) * EC + 4 * c4;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4* src = slots + static_cast<size_t>(tail) * split_s * kPerTile + r;
+  for (int q = 0; q < split_s; ++q) {
+    const float4 v = __ldcs(src + static_cast<size_t>(q) * kPerTile);
+    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+  }
+  if (row >= m || col >= n) return;
+  OutT* dst = out + static_cast<size_t>(row) * n + col;
+  const float v4[4] = {sum.x, sum.y, sum.z, sum.w};
+  if (vec_ok && col + 4 <= n) {
+    if constexpr (std::is_same<OutT, float>::value) {
+      *reinterpret_cast<float4*>(dst) = sum;
+    } else {
+      OutT o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = from_f32<OutT>(v4[j]);
+      *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (col + j < n) dst[j] = from_f32<OutT>(v4[j]);
+  }
+}
+
 // ------------------------------- host side --------------------------------
 // Byte tensor of rank 2 or 3 (innermost first), 128-byte swizzled boxes.
 bool encode_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
@@ -602,6 +610,15 @@ ks_status_t launch_one(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUte
     if (tma_encode(&tm_c, dt, 2, a.out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) p.tma_store = 1;
   }
   kernel<<<grid, C::kThreads, C::smem_bytes(GROUPED), stream>>>(tm_a, tm_b, tm_c, p);
+  if constexpr (!GROUPED) {
+    if (p.split_s > 1) {
+      const int tails = p.split_items / p.split_s;
+      const int work = tails * C::kEpiWarps * (C::kEpiCols / 4) * 32;
+      split_reduce_kernel<BN, OutT><<<(work + 255) / 256, 256, 0, stream>>>(
+          static_cast<OutT*>(p.out), p.split_slots, p.split_from, p.split_s, tails, p.tiles_m, p.tiles_n, p.m, p.n,
+          p.vec_store);
+    }
+  }
   return cuda_status(cudaGetLastError(), a.where);
 }
 
@@ -703,29 +720,19 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
   p.split_items = 0;
   p.split_s = 1;
   p.split_slots = nullptr;
-  p.split_counters = nullptr;
   if (!grouped && a.force_split != 0 && tiles > grid) {
     const int rem = static_cast<int>(tiles % grid);
     int s = rem > 0 ? grid / rem : 1;
     if (s > 8) s = 8;
     while (s > 1 && p.nkb / s < 4) --s;
     if (rem > 0 && s >= 2) {
-      const int epi_warps = bn == 256 ? Cfg<256>::kEpiWarps : Cfg<128>::kEpiWarps;
-      const int epi_cols = bn == 256 ? Cfg<256>::kEpiCols : Cfg<128>::kEpiCols;
       const size_t slot_bytes = static_cast<size_t>(rem) * s * kBM * bn * sizeof(float);
-      const size_t counter_bytes = static_cast<size_t>(rem) * epi_warps * (epi_cols / 32) * sizeof(unsigned int);
       float4* slots = static_cast<float4*>(stream_scratch(stream, slot_bytes, 2));
-      unsigned int* counters = static_cast<unsigned int*>(stream_scratch(stream, counter_bytes, 3));
-      if (slots != nullptr && counters != nullptr) {
-        if (stream_scratch_take_dirty(stream, 3)) {
-          cudaError_t e = cudaMemsetAsync(counters, 0, stream_scratch_bytes(stream, 3), stream);
-          if (e != cudaSuccess) return cuda_status(e, a.where);
-        }
+      if (slots != nullptr) {
         p.split_from = static_cast<int>(tiles) - rem;
         p.split_items = rem * s;
         p.split_s = s;
         p.split_slots = slots;
-        p.split_counters = counters;
       }
     }
   }
