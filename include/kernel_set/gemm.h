@@ -2,10 +2,11 @@
  * Quantized GEMM entry points: FP8 with fine-grained fp32 scales, and int4
  * weight-only with 16-bit activations.
  *
- * Replaces the two quantized entries of include/kernel_set/gemm.h of the
- * reference project (ks_gemm_w4a16 at :51-59, ks_gemm_fp8_blockwise at
- * :79-98). The dense / int8 / per-token-fp8 / nvfp4 GEMMs of that header are
- * a different code path and are not exported by this library.
+ * Replaces the quantized entries of include/kernel_set/gemm.h of the
+ * reference project (ks_gemm_w8a8 at :39-49, ks_gemm_w4a16 at :51-59,
+ * ks_gemm_fp8 at :60-77, ks_gemm_fp8_blockwise at :79-98). The dense, batched
+ * and nvfp4 GEMMs of that header are a different code path and are exported
+ * only as NOT_IMPLEMENTED stubs.
  *
  * All matrices are row-major and dense (row stride = number of columns). All
  * pointers are device pointers. Calls enqueue work on `stream` and return
@@ -78,6 +79,37 @@ KS_API ks_status_t ks_gemm_w4a16_static_scratch(void* c, const void* a,
                                                 int group_size,
                                                 ks_dtype_t dtype,
                                                 ks_stream_t stream);
+
+/*
+ * 8-bit GEMMs with one scale per row of A and one per column of B:
+ *   C = (a_scale (x) b_scale) * (A @ B) [+ bias]
+ *   a        [M,K]  fp8 (e4m3 / e5m2, `fp8_dtype`) resp. int8
+ *   b        [K,N]  same type, row-major (the transposed, quantized weight)
+ *   a_scale  [M] with KS_QUANT_PER_TOKEN, [1] with KS_QUANT_PER_TENSOR   (fp32)
+ *   b_scale  [N] with KS_QUANT_PER_CHANNEL, [1] with KS_QUANT_PER_TENSOR (fp32)
+ *   bias     [N] in `out_dtype` or NULL (ks_gemm_w8a8 only)
+ *   out / c  [M,N]  f32 / f16 / bf16
+ * The products are accumulated in fp32 (fp8) resp. exactly in int32 (int8); the
+ * result is (acc * a_scale) * b_scale [+ bias], rounded once. Other modes are
+ * INVALID_ARGUMENT. K and N multiples of 16 with 16-byte aligned operands take
+ * the tcgen05 kernel (kind::f8f6f4 / kind::i8, the whole K range accumulated
+ * in tensor memory); everything else a slower general kernel.
+ * Same contracts as the reference: gemm.h:60-77 with gemm_fp8.cu:147-153, and
+ * gemm.h:39-49 with gemm_w8a8.cu:134-141, 160-190.
+ */
+KS_API ks_status_t ks_gemm_fp8(void* out, const void* a_fp8, const void* b_fp8,
+                               const float* a_scale, const float* b_scale,
+                               int64_t m, int64_t n, int64_t k,
+                               ks_quant_mode_t a_mode, ks_quant_mode_t b_mode,
+                               ks_dtype_t fp8_dtype, ks_dtype_t out_dtype,
+                               ks_stream_t stream);
+
+KS_API ks_status_t ks_gemm_w8a8(void* c, const void* a_i8, const void* b_i8,
+                                const float* a_scale, const float* b_scale,
+                                const void* bias, int64_t m, int64_t n,
+                                int64_t k, ks_quant_mode_t a_mode,
+                                ks_quant_mode_t b_mode, ks_dtype_t out_dtype,
+                                ks_stream_t stream);
 
 /*
  * out[m,n] = sum over K-blocks kb of

@@ -141,6 +141,25 @@ KS_API ks_status_t ks_moe_grouped_gemm_fp8_blockwise(
     int b_layout, ks_dtype_t fp8_dtype, ks_dtype_t out_dtype,
     ks_stream_t stream);
 
+/*
+ * The same product over the masked layout that CUDA-graph decode uses: every
+ * expert owns a fixed slab of max_m rows and computes only its first
+ * masked_m[e] of them, so the launch does not depend on the routing.
+ *   a_fp8    [E, max_m, K]            a_scale [E, max_m, ceil(K/bk)]
+ *   masked_m [E] int32 on the device  (values are clamped to [0, max_m])
+ *   out      [E, max_m, N]; rows at or beyond masked_m[e] are left untouched
+ *   b_fp8 / b_scale / b_layout as above.
+ * Needs block_n = block_k = 128 (UNSUPPORTED_SHAPE otherwise). The reference
+ * reaches this layout only through an external provider
+ * (backends/_registry.py:1686-1689); it has no C entry for it.
+ */
+KS_API ks_status_t ks_moe_grouped_gemm_fp8_blockwise_masked(
+    void* out, const void* a_fp8, const void* b_fp8, const float* a_scale,
+    const float* b_scale, const int32_t* masked_m, int num_experts,
+    int64_t max_m, int64_t n, int64_t k, int block_n, int block_k,
+    int b_layout, ks_dtype_t fp8_dtype, ks_dtype_t out_dtype,
+    ks_stream_t stream);
+
 KS_END_EXTERN_C
 
 #endif /* KERNEL_SET_MOE_H_ */

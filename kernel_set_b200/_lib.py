@@ -161,6 +161,9 @@ _decl("ks_gemm_w4a16", _W4A16)
 _decl("ks_gemm_w4a16_static_scratch", _W4A16)
 _FP8_BW = [_VP, _VP, _VP, POINTER(c_float), POINTER(c_float), c_int64, c_int64, c_int64,
            c_int, c_int, c_int, c_int, _VP]
+_SCALED = [_VP, _VP, _VP, POINTER(c_float), POINTER(c_float)]
+_decl("ks_gemm_fp8", _SCALED + [c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, _VP])
+_decl("ks_gemm_w8a8", _SCALED + [_VP, c_int64, c_int64, c_int64, c_int, c_int, c_int, _VP])
 _decl("ks_gemm_fp8_blockwise", _FP8_BW)
 _decl("ks_gemm_fp8_blockwise_nt", _FP8_BW)
 
@@ -184,6 +187,9 @@ _decl("ks_moe_grouped_gemm_fp8_blockwise",
 _decl("ks_swiglu", [_VP, _VP, _VP, c_int64, c_int64, c_int, _VP])
 _decl("ks_swiglu_packed", [_VP, _VP, c_int64, c_int64, c_int, _VP])
 _decl("ks_swiglu_packed_quant_fp8", [_VP, POINTER(c_float), _VP, c_int64, c_int64, c_int, c_int, _VP])
+_decl("ks_moe_grouped_gemm_fp8_blockwise_masked",
+      [_VP, _VP, _VP, POINTER(c_float), POINTER(c_float), POINTER(c_int32), c_int, c_int64, c_int64, c_int64,
+       c_int, c_int, c_int, c_int, c_int, _VP])
 
 
 def status_string(status: int) -> str:

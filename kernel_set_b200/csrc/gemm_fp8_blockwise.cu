@@ -169,4 +169,41 @@ ks_status_t ks_moe_grouped_gemm_fp8_blockwise(void* out, const void* a_fp8, cons
   return run(a, stream);
 }
 
+ks_status_t ks_moe_grouped_gemm_fp8_blockwise_masked(void* out, const void* a_fp8, const void* b_fp8,
+                                                     const float* a_scale, const float* b_scale,
+                                                     const int32_t* masked_m, int num_experts, int64_t max_m,
+                                                     int64_t n, int64_t k, int block_n, int block_k, int b_layout,
+                                                     ks_dtype_t fp8_dtype, ks_dtype_t out_dtype,
+                                                     ks_stream_t stream) {
+  using namespace ksb;
+  const char* where = "ks_moe_grouped_gemm_fp8_blockwise_masked";
+  if (masked_m == nullptr) KSB_FAIL(KS_ERROR_INVALID_ARGUMENT, "null arg: masked_m");
+  if (num_experts <= 0 || max_m <= 0) KSB_FAIL(KS_ERROR_INVALID_ARGUMENT, std::string(where) + ": bad shape");
+  if (b_layout != 0 && b_layout != 1)
+    KSB_FAIL(KS_ERROR_INVALID_ARGUMENT, std::string(where) + ": b_layout must be 0 ([E,K,N]) or 1 ([E,N,K])");
+  if (max_m > INT32_MAX / num_experts)
+    KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE, std::string(where) + ": num_experts * max_m exceeds int32 range");
+  ks_status_t st = check_common(where, out, a_fp8, b_fp8, a_scale, b_scale, max_m * num_experts, n, k, block_n,
+                                block_k, fp8_dtype, out_dtype, false);
+  if (st != KS_SUCCESS) return st;
+  st = require_sm100(where);
+  if (st != KS_SUCCESS) return st;
+  st = poll_kernel_fault(where);
+  if (st != KS_SUCCESS) return st;
+  sm100::Fp8GemmArgs a;
+  a.where = where; a.out = out; a.a = a_fp8; a.b = b_fp8; a.a_scale = a_scale; a.b_scale = b_scale;
+  a.masked_m = masked_m; a.max_m = max_m; a.num_experts = num_experts;
+  a.m = max_m * num_experts; a.n = n; a.k = k; a.block_n = block_n; a.block_k = block_k; a.nt = b_layout == 1;
+  a.e5m2 = fp8_dtype == KS_DTYPE_F8E5M2; a.out_dtype = out_dtype;
+  const EnvChoice env = env_choice();
+  a.force_bn = env.bn;
+  // the row counts live on the device (that is the point of the layout: the launch does not
+  // depend on them), so only the tcgen05 kernel, which reads them itself, serves this entry
+  if (!sm100::fp8_blockwise_eligible(a))
+    KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE,
+             std::string(where) + ": needs 128 x 128 scale blocks, K (and N for [E,K,N]) multiples of 16, "
+                                  "16-byte aligned operands and at most 1024 experts");
+  return sm100::launch_fp8_blockwise(a, as_stream(stream));
+}
+
 }  // extern "C"

@@ -55,9 +55,7 @@ KSB_NOT_IMPLEMENTED(ks_embedding_lookup)
 KSB_NOT_IMPLEMENTED(ks_gemm)
 KSB_NOT_IMPLEMENTED(ks_gemm_batched)
 KSB_NOT_IMPLEMENTED(ks_gemm_bias_act)
-KSB_NOT_IMPLEMENTED(ks_gemm_fp8)
 KSB_NOT_IMPLEMENTED(ks_gemm_nvfp4)
-KSB_NOT_IMPLEMENTED(ks_gemm_w8a8)
 
 // linear_attn.h
 KSB_NOT_IMPLEMENTED(ks_gated_delta_rule)

@@ -51,6 +51,59 @@ template <> struct Vec16<float> {
   }
 };
 
+// The same 16 elements as raw 16-byte words, so that a load can be issued long before its
+// conversion: Raw16<T>::load now, Raw16<T>::unpack later.
+template <typename T> struct Raw16 {
+  uint4 a, b;
+  __device__ static Raw16 load(const T* p) {
+    Raw16 r;
+    r.a = __ldg(reinterpret_cast<const uint4*>(p));
+    r.b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+    return r;
+  }
+  __device__ static Raw16 zero() {
+    Raw16 r;
+    r.a = make_uint4(0u, 0u, 0u, 0u);
+    r.b = r.a;
+    return r;
+  }
+  __device__ void unpack(float (&v)[16]) const {
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if constexpr (sizeof(T) == 2 && !__is_same(T, __half)) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+      }
+    }
+  }
+};
+template <> struct Raw16<float> {
+  float4 q[4];
+  __device__ static Raw16 load(const float* p) {
+    Raw16 r;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r.q[i] = __ldg(reinterpret_cast<const float4*>(p) + i);
+    return r;
+  }
+  __device__ static Raw16 zero() {
+    Raw16 r;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r.q[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    return r;
+  }
+  __device__ void unpack(float (&v)[16]) const {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[4 * i] = q[i].x; v[4 * i + 1] = q[i].y; v[4 * i + 2] = q[i].z; v[4 * i + 3] = q[i].w;
+    }
+  }
+};
+
 // Two fp32 -> two fp8 codes (low byte = first value), RNE, saturating.
 template <bool E5M2>
 __device__ __forceinline__ uint32_t cvt_pair(float lo, float hi) {

@@ -108,10 +108,10 @@ struct Cfg {
   // Dense problems stage the finished tile for TMA stores: 32 rows x 128 B per epilogue warp.
   static constexpr int kStoreStageBytes = 32 * 128;
   // ring + 1024 B alignment slack + barriers/flags, then either the store staging
-  // (dense) or the tile prefix and offsets (grouped)
+  // (dense) or the tile prefix, first rows and end rows of the experts (grouped)
   static constexpr int smem_bytes(bool grouped) {
     return kStages * kStageBytes + 1024 + 256 +
-           (grouped ? 2 * 4 * (kMaxExperts + 1) : kEpiWarps * kStoreStageBytes);
+           (grouped ? 3 * 4 * (kMaxExperts + 1) : kEpiWarps * kStoreStageBytes);
   }
 };
 
@@ -136,6 +136,13 @@ struct Params {
   int split_items;        // number of K-part items (tail tiles x split_s), at most the grid size
   int split_s;            // 1 = no split
   float4* split_slots;    // [tail tile][part][epilogue warp][16-byte column chunk][lane]
+  // MODE 1 / 2 (one scale per row and per column, the whole K range accumulated in TMEM)
+  const void* bias;       // [N] in the output type or NULL
+  int a_per_row;          // a_scale is [M] (else one value)
+  int b_per_col;          // b_scale is [N] (else one value)
+  // grouped, masked layout: expert e owns rows [e * max_m, e * max_m + masked_m[e])
+  const int32_t* masked_m;
+  int max_m;
 };
 
 struct TileCoord {
@@ -192,7 +199,7 @@ __device__ __forceinline__ bool locate_tile(const Params& p, const int* prefix, 
     }
     tc->expert = lo;
     tc->row0 = offs[lo] + (mt - prefix[lo]) * kBM;
-    tc->row_end = offs[lo + 1];
+    tc->row_end = offs[kMaxExperts + 1 + lo];   // ends[lo]
     tc->n0 = (t - mt * p.tiles_n) * BN;
     return true;
   }
@@ -221,7 +228,11 @@ static_assert(128 * Cfg<256>::kRegsIssue + (Cfg<256>::kThreads - 128) * Cfg<256>
                   Cfg<256>::kThreads * ((65536 / Cfg<256>::kThreads) & ~7),
               "setmaxnreg budgets exceed the register pool the CTA is launched with");
 
-template <int BN, bool NT, bool GROUPED, typename OutT>
+// MODE 0: block-scaled FP8 (a partial per K-block, promoted in registers).
+// MODE 1: FP8 with one scale per row of A and one per column of B: the whole K range
+//         accumulates in tensor memory, the epilogue runs once per tile.
+// MODE 2: the same with int8 operands (kind::i8, int32 accumulators) and an optional bias.
+template <int BN, bool NT, bool GROUPED, typename OutT, int MODE = 0>
 __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
 fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                           const __grid_constant__ CUtensorMap tm_c, const Params p) {
@@ -238,7 +249,8 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
   const uint32_t bar_full = ctrl_addr;
   const uint32_t bar_empty = ctrl_addr + 8 * C::kStages;
   const uint32_t bar_tempty = ctrl_addr + 16 * C::kStages;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * C::kStages + 8 * C::kAccBufs);
+  const uint32_t bar_accfull = bar_tempty + 8 * C::kAccBufs;   // MODE 1 / 2: a tile's accumulator is complete
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * C::kStages + 16 * C::kAccBufs);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   int* prefix = reinterpret_cast<int*>(ctrl + 256);
   int* offs = prefix + (kMaxExperts + 1);
@@ -254,6 +266,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     }
     for (int b = 0; b < C::kAccBufs; ++b) {
       mbar_init(bar_tempty + 8 * b, C::kEpiWarps);
+      mbar_init(bar_accfull + 8 * b, 1);
     }
     *abort_flag = 0u;
     fence_barrier_init();
@@ -266,13 +279,28 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     tmem_relinquish();
   }
   if constexpr (GROUPED) {
-    for (int e = threadIdx.x; e <= p.num_experts; e += blockDim.x) offs[e] = p.offsets[e];
+    // offs[e] = first row of expert e; with the masked layout the rows of an expert end at
+    // offs[e] + masked_m[e] instead of at offs[e + 1] (ends[] holds either)
+    int* ends = offs + (kMaxExperts + 1);
+    for (int e = threadIdx.x; e <= p.num_experts; e += blockDim.x) {
+      if (p.masked_m != nullptr) {
+        offs[e] = e * p.max_m;
+        if (e < p.num_experts) {
+          int mm = p.masked_m[e];
+          mm = mm < 0 ? 0 : (mm > p.max_m ? p.max_m : mm);
+          ends[e] = e * p.max_m + mm;
+        }
+      } else {
+        offs[e] = p.offsets[e];
+        if (e < p.num_experts) ends[e] = p.offsets[e + 1];
+      }
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
       int run = 0;
       for (int e = 0; e < p.num_experts; ++e) {
         prefix[e] = run;
-        const int rows = offs[e + 1] - offs[e];
+        const int rows = ends[e] - offs[e];
         run += rows > 0 ? (rows + kBM - 1) / kBM : 0;
       }
       prefix[p.num_experts] = run;
@@ -314,15 +342,22 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     // ------------------------------- MMA issuer -------------------------------
     if constexpr (C::kRebalanceRegs) setmaxnreg_dec<C::kRegsIssue>();
     uint32_t it = 0;
+    uint32_t tile_n = 0;   // MODE 1 / 2: tiles so far (one accumulator buffer per tile)
     bool ok = true;
     TileCoord tc;
     for (ItemWalk walk(p); ok && walk.template next<BN, GROUPED>(p, prefix, offs, &tc);) {
+      if constexpr (MODE != 0) {
+        const uint32_t tbuf = tile_n % C::kAccBufs, tph = (tile_n / C::kAccBufs) & 1u;
+        if (!mbar_wait(wctx, bar_tempty + 8 * tbuf, tph ^ 1u, 0x200u + tbuf)) { ok = false; break; }
+      }
       for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
         const uint32_t s = it % C::kStages;
         const uint32_t ph = (it / C::kStages) & 1u;
-        const uint32_t buf = it % C::kAccBufs;
-        const uint32_t aph = (it / C::kAccBufs) & 1u;
-        if (!mbar_wait(wctx, bar_tempty + 8 * buf, aph ^ 1u, 0x200u + buf)) { ok = false; break; }
+        const uint32_t buf = MODE != 0 ? tile_n % C::kAccBufs : it % C::kAccBufs;
+        if constexpr (MODE == 0) {
+          const uint32_t aph = (it / C::kAccBufs) & 1u;
+          if (!mbar_wait(wctx, bar_tempty + 8 * buf, aph ^ 1u, 0x200u + buf)) { ok = false; break; }
+        }
         if (!mbar_wait(wctx, bar_full + 8 * s, ph, 0x300u + s)) { ok = false; break; }
         tc_fence_after_sync();
         {
@@ -339,11 +374,17 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
             const uint64_t a_desc = umma_smem_desc_sw128(a_src + kk * 32, 16, 1024);
             const uint64_t b_desc = NT ? umma_smem_desc_sw128(b_src + kk * 32, 16, 1024)
                                        : umma_smem_desc_sw128(b_src + kk * 32 * 128, 128 * kBK, 1024);
-            umma_f8f6f4_elect(d_tmem, a_desc, b_desc, p.idesc, kk > 0 ? 1u : 0u);
+            const uint32_t accumulate = (kk > 0 || (MODE != 0 && kb > tc.kb0)) ? 1u : 0u;
+            if constexpr (MODE == 2) umma_i8_elect(d_tmem, a_desc, b_desc, p.idesc, accumulate);
+            else umma_f8f6f4_elect(d_tmem, a_desc, b_desc, p.idesc, accumulate);
           }
           tc_commit_elect(bar_empty + 8 * s);
+          if constexpr (MODE != 0) {
+            if (kb == tc.kb1 - 1) tc_commit_elect(bar_accfull + 8 * buf);
+          }
         }
       }
+      ++tile_n;
     }
   } else if (warp >= 4) {
     // -------------------------------- epilogue --------------------------------
@@ -354,6 +395,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     const int row_in_tile = quarter * 32 + lane;
     OutT* out = static_cast<OutT*>(p.out);
     uint32_t it = 0;
+    uint32_t tile_n = 0;   // MODE 1 / 2: tiles so far
     bool ok = true;
     TileCoord tc;
     for (ItemWalk walk(p); ok && walk.template next<BN, GROUPED>(p, prefix, offs, &tc);) {
@@ -371,6 +413,41 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
 #pragma unroll
       for (int i = 0; i < EC / 2; ++i) acc[i] = make_float2(0.f, 0.f);
 
+      if constexpr (MODE != 0) {
+        // the tile's accumulator is complete: scale by a_scale[row] * b_scale[col] (and add
+        // the bias) on the way out of tensor memory, as kernels/src/gemm/gemm_fp8.cu:147-153
+        // and gemm_w8a8.cu:134-141 of the reference do
+        const uint32_t tbuf = tile_n % C::kAccBufs, tph = (tile_n / C::kAccBufs) & 1u;
+        ++tile_n;
+        if (!mbar_wait_long(wctx, bar_accfull + 8 * tbuf, tph, 0x400u + tbuf)) { ok = false; break; }
+        tc_fence_after_sync();
+        const float a_sc = (p.a_per_row && row_ok) ? __ldg(p.a_scale + row) : __ldg(p.a_scale);
+        const float b_one = __ldg(p.b_scale);
+        const OutT* bias = static_cast<const OutT*>(p.bias);
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tbuf * BN + slice * EC;
+#pragma unroll
+        for (int c = 0; c < EC / 16; ++c) {
+          uint32_t r[16];
+          tmem_ld(taddr + c * 16, r);
+          tmem_wait_ld(r);
+          if (c == EC / 16 - 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * tbuf);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int col = col0 + c * 16 + j;
+            const bool col_ok = col < p.n;
+            const float b_sc = (p.b_per_col && col_ok) ? __ldg(p.b_scale + col) : b_one;
+            const float raw = MODE == 2 ? static_cast<float>(static_cast<int32_t>(r[j])) : __uint_as_float(r[j]);
+            float v = __fmul_rn(__fmul_rn(raw, a_sc), b_sc);
+            if (bias != nullptr && col_ok) v = __fadd_rn(v, to_f32<OutT>(bias[col]));
+            if (j & 1) acc[c * 8 + (j >> 1)].y = v; else acc[c * 8 + (j >> 1)].x = v;
+          }
+        }
+      }
+
       // Scales are fetched two K-blocks at a time, one group ahead of use: an
       // L2 round trip is longer than one K-block, so a load issued for the next
       // block alone would sit on the critical path.
@@ -386,9 +463,9 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
           bs_nxt[j] = in ? __ldg(bs_ptr + static_cast<size_t>(kb) * bs_step) : 0.f;
         }
       };
-      fetch_scales(tc.kb0);
+      if constexpr (MODE == 0) fetch_scales(tc.kb0);
 
-      for (int kb0 = tc.kb0; kb0 < tc.kb1 && ok; kb0 += G) {
+      for (int kb0 = tc.kb0; MODE == 0 && kb0 < tc.kb1 && ok; kb0 += G) {
         float sc[G];
 #pragma unroll
         for (int j = 0; j < G; ++j) sc[j] = as_nxt[j] * bs_nxt[j];
@@ -578,11 +655,11 @@ bool encode_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dim
                     CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-template <int BN, bool NT, bool GROUPED, typename OutT>
+template <int BN, bool NT, bool GROUPED, typename OutT, int MODE = 0>
 ks_status_t launch_one(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUtensorMap& tm_b, Params p,
                        int grid, cudaStream_t stream) {
   using C = Cfg<BN>;
-  auto kernel = fp8_blockwise_umma_kernel<BN, NT, GROUPED, OutT>;
+  auto kernel = fp8_blockwise_umma_kernel<BN, NT, GROUPED, OutT, MODE>;
   static std::mutex mu;
   static bool attr_done[64] = {};
   int dev = 0;
@@ -622,20 +699,23 @@ ks_status_t launch_one(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUte
   return cuda_status(cudaGetLastError(), a.where);
 }
 
-template <int BN, bool NT, bool GROUPED>
+template <int BN, bool NT, bool GROUPED, int MODE = 0>
 ks_status_t launch_out(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUtensorMap& tm_b, const Params& p,
                        int grid, cudaStream_t stream) {
   switch (a.out_dtype) {
-    case KS_DTYPE_F32: return launch_one<BN, NT, GROUPED, float>(a, tm_a, tm_b, p, grid, stream);
-    case KS_DTYPE_F16: return launch_one<BN, NT, GROUPED, __half>(a, tm_a, tm_b, p, grid, stream);
-    default: return launch_one<BN, NT, GROUPED, __nv_bfloat16>(a, tm_a, tm_b, p, grid, stream);
+    case KS_DTYPE_F32: return launch_one<BN, NT, GROUPED, float, MODE>(a, tm_a, tm_b, p, grid, stream);
+    case KS_DTYPE_F16: return launch_one<BN, NT, GROUPED, __half, MODE>(a, tm_a, tm_b, p, grid, stream);
+    default: return launch_one<BN, NT, GROUPED, __nv_bfloat16, MODE>(a, tm_a, tm_b, p, grid, stream);
   }
 }
 
 template <int BN>
 ks_status_t launch_bn(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUtensorMap& tm_b, const Params& p,
                       int grid, cudaStream_t stream) {
-  const bool grouped = a.offsets != nullptr;
+  const bool grouped = a.offsets != nullptr || a.masked_m != nullptr;
+  // the per-row / per-column scaled kernels exist for the reference's layout (B stored [K,N]), dense
+  if (a.mode == 1) return launch_out<BN, false, false, 1>(a, tm_a, tm_b, p, grid, stream);
+  if (a.mode == 2) return launch_out<BN, false, false, 2>(a, tm_a, tm_b, p, grid, stream);
   if (a.nt) return grouped ? launch_out<BN, true, true>(a, tm_a, tm_b, p, grid, stream)
                            : launch_out<BN, true, false>(a, tm_a, tm_b, p, grid, stream);
   return grouped ? launch_out<BN, false, true>(a, tm_a, tm_b, p, grid, stream)
@@ -645,17 +725,19 @@ ks_status_t launch_bn(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUten
 }  // namespace
 
 bool fp8_blockwise_eligible(const Fp8GemmArgs& a) {
-  if (a.block_n != 128 || a.block_k != 128) return false;
+  if (a.mode == 0 && (a.block_n != 128 || a.block_k != 128)) return false;
+  if (a.mode != 0 && (a.nt || a.offsets != nullptr || a.masked_m != nullptr)) return false;
   if (a.k % 16 != 0) return false;
   if (!a.nt && a.n % 16 != 0) return false;
   if (!aligned16(a.a) || !aligned16(a.b)) return false;
   if (a.m > INT32_MAX / 2 || a.n > INT32_MAX / 2 || a.k > INT32_MAX / 2) return false;
-  if (a.offsets != nullptr && (a.num_experts > kMaxExperts || a.num_experts < 1)) return false;
+  if ((a.offsets != nullptr || a.masked_m != nullptr) && (a.num_experts > kMaxExperts || a.num_experts < 1)) return false;
+  if (a.masked_m != nullptr && (a.max_m < 1 || a.max_m * a.num_experts != a.m)) return false;
   return tma_available();
 }
 
 ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
-  const bool grouped = a.offsets != nullptr;
+  const bool grouped = a.offsets != nullptr || a.masked_m != nullptr;
   const int experts = grouped ? a.num_experts : 1;
   const int sms = sm_count();
   const int64_t tiles_m_bound = grouped ? (a.m + kBM - 1) / kBM + experts : (a.m + kBM - 1) / kBM;
@@ -664,8 +746,10 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
   // as soon as they do not need more rounds than narrow ones would save.
   const int64_t tiles256 = tiles_m_bound * ((a.n + 255) / 256);
   const int64_t tiles128 = tiles_m_bound * ((a.n + 127) / 128);
-  const int64_t cost256 = ((tiles256 + sms - 1) / sms) * 850;
-  const int64_t cost128 = ((tiles128 + sms - 1) / sms) * 550;
+  // (with one scale per row and column nothing is promoted per K-block: the MMAs run back to
+  // back, ~512 / ~300 cycles per K-block, and the wide tile wins whenever it needs no more rounds)
+  const int64_t cost256 = ((tiles256 + sms - 1) / sms) * (a.mode == 0 ? 850 : 512);
+  const int64_t cost128 = ((tiles128 + sms - 1) / sms) * (a.mode == 0 ? 550 : 300);
   const int bn = (a.force_bn == 128 || a.force_bn == 256) ? a.force_bn : (cost256 <= cost128 ? 256 : 128);
 
   CUtensorMap tm_a, tm_b;
@@ -695,6 +779,11 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
   p.a_scale = a.a_scale;
   p.b_scale = a.b_scale;
   p.offsets = a.offsets;
+  p.masked_m = a.masked_m;
+  p.max_m = static_cast<int>(a.max_m);
+  p.bias = a.bias;
+  p.a_per_row = a.a_per_row ? 1 : 0;
+  p.b_per_col = a.b_per_col ? 1 : 0;
   p.fault_word = kernel_fault_word();
   p.num_experts = experts;
   p.m = static_cast<int>(a.m);
@@ -704,8 +793,10 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
   p.nnb = static_cast<int>((a.n + 127) / 128);
   p.tiles_n = static_cast<int>((a.n + bn - 1) / bn);
   p.tiles_m = static_cast<int>((a.m + kBM - 1) / kBM);
-  const uint32_t fmt = a.e5m2 ? 1u : 0u;
-  p.idesc = umma_instr_desc(fmt, fmt, 0u, a.nt ? 0u : 1u, kBM, static_cast<uint32_t>(bn));
+  // operand formats: e4m3 / e5m2 for the fp8 kinds; signed 8-bit integers with an int32
+  // accumulator for kind::i8
+  const uint32_t fmt = a.mode == 2 ? 1u : (a.e5m2 ? 1u : 0u);
+  p.idesc = umma_instr_desc(fmt, fmt, 0u, a.nt ? 0u : 1u, kBM, static_cast<uint32_t>(bn), a.mode == 2 ? 2u : 1u);
   const size_t out_elt = a.out_dtype == KS_DTYPE_F32 ? 4 : 2;
   p.vec_store = (aligned16(a.out) && (static_cast<size_t>(a.n) * out_elt) % 16 == 0) ? 1 : 0;
 
@@ -720,7 +811,7 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
   p.split_items = 0;
   p.split_s = 1;
   p.split_slots = nullptr;
-  if (!grouped && a.force_split != 0 && tiles > grid) {
+  if (!grouped && a.mode == 0 && a.force_split != 0 && tiles > grid) {
     const int rem = static_cast<int>(tiles % grid);
     int s = rem > 0 ? grid / rem : 1;
     if (s > 8) s = 8;

@@ -25,6 +25,16 @@ struct Fp8GemmArgs {
   ks_dtype_t out_dtype = KS_DTYPE_BF16;
   int force_bn = 0;                // 128 / 256 pins the tile width (tests), 0 = choose
   int force_split = -1;            // K-split of the last partial round: -1 choose, 0 never, 1 whenever legal
+  // Grouped, masked layout (a and out are [E, max_m, .]; expert e uses its first masked_m[e]
+  // rows): set masked_m and max_m instead of offsets; m = E * max_m.
+  const int32_t* masked_m = nullptr;
+  int64_t max_m = 0;
+  // mode 0: block scales as above. mode 1: fp8 operands, a_scale [m] or [1], b_scale [n] or
+  // [1] (kernels/src/gemm/gemm_fp8.cu of the reference). mode 2: int8 operands, same scales,
+  // optional bias [n] in the output type (gemm_w8a8.cu).
+  int mode = 0;
+  bool a_per_row = false, b_per_col = false;
+  const void* bias = nullptr;
 };
 
 // True when the tcgen05 kernel can take the problem (128 x 128 scale blocks,

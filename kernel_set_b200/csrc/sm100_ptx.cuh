@@ -338,12 +338,14 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
-// 32-bit instruction descriptor, dense, fp32 accumulate. Formats: for
-// kind::f8f6f4 0 = e4m3, 1 = e5m2; for kind::f16 0 = f16, 1 = bf16.
-// major: 0 = K-major operand, 1 = MN-major operand.
+// 32-bit instruction descriptor, dense. Formats: for kind::f8f6f4 0 = e4m3,
+// 1 = e5m2; for kind::f16 0 = f16, 1 = bf16; for kind::i8 0 = unsigned, 1 = signed.
+// major: 0 = K-major operand, 1 = MN-major operand. acc_fmt: 1 = fp32 accumulator
+// (the floating-point kinds), 2 = int32 (kind::i8).
 __host__ __device__ constexpr uint32_t umma_instr_desc(uint32_t a_fmt, uint32_t b_fmt, uint32_t a_mn_major,
-                                                       uint32_t b_mn_major, uint32_t m, uint32_t n) {
-  return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
+                                                       uint32_t b_mn_major, uint32_t m, uint32_t n,
+                                                       uint32_t acc_fmt = 1u) {
+  return (acc_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
          ((m >> 4) << 24);
 }
 
@@ -386,6 +388,15 @@ __device__ __forceinline__ void umma_f8f6f4_elect(uint32_t d_tmem, uint64_t a_de
   asm volatile("{\n\t.reg .pred p;\n\t" KSB_ELECT_PROLOGUE
                "setp.ne.b32 p, %4, 0;\n\t"
                "@q tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+// int8 x int8 -> int32 (signedness of each operand comes from the instruction descriptor)
+__device__ __forceinline__ void umma_i8_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t" KSB_ELECT_PROLOGUE
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "@q tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
                "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
                : "memory");
 }

@@ -872,9 +872,20 @@ ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, unsigned int* c
 
 }  // namespace
 
-// The register-operand decode kernel takes every problem it can, unless the caller pinned
-// the tcgen05 kernel.
-bool use_decode_kernel(const W4A16Args& a) { return a.kernel != 1 && decode::eligible(a); }
+// Which fast kernel. The register-operand decode kernel feeds legacy mma.sync, whose rate on
+// this part is about a tenth of tcgen05's (measured: ~100 bf16 FMA per clock and SM
+// sub-partition): with 8 tokens (one MMA per 16 x 16 weight block) it is ahead of the tcgen05
+// kernel on wide weights (K=4096, N=28672: 28.9 us against 33.7), at 16 tokens they are level,
+// beyond that it is MMA-bound (32 tokens: 46 us against 37). On problems with few units per
+// CTA (K=14336, N=4096: 6 per CTA) its pipeline fill and the split-K fix-up of every CTA cost
+// more than they save (24.7 us against 22.8). Chosen: at most 8 tokens and at least 10 units
+// per CTA; the caller can pin either kernel.
+bool use_decode_kernel(const W4A16Args& a) {
+  if (a.kernel == 1 || !decode::eligible(a)) return false;
+  if (a.kernel == 2 || !w4a16_eligible(a)) return true;
+  const long long units = ((a.n + 255) / 256) * (a.k / 128);
+  return a.m <= 8 && units >= 20ll * sm_count();
+}
 
 ks_status_t launch_w4a16(const W4A16Args& a, cudaStream_t stream) {
   // Counters and slots are separate allocations: the counters must be zero whenever no

@@ -30,8 +30,9 @@
 //     and one packed multiply by the scale finish them, bit-identical to the
 //     torch statement for integer zero-points (others take an fp32 path);
 //   * the k order inside a 16-k block is permuted (slot pairs hold k = 4s, 4s+2
-//     and 4s+1, 4s+3); the activation fragment is permuted to match with two
-//     byte-permutes;
+//     and 4s+1, 4s+3); the thread that copied an activation chunk puts it into that
+//     order in shared memory once, so that the consumers' 8-byte loads are the B
+//     fragments as they are;
 //   * tokens are the n8 dimension of the MMA: 8 tokens per instruction, MG
 //     instructions for up to 8*MG tokens.
 // Work is cut stream-K style: (column tile, K-step) units are dealt to the CTAs
@@ -71,7 +72,7 @@ struct Cfg {
   // between dependent instructions, and the __syncthreads of one CTA overlaps the other's
   // work. Their rings together keep 100+ KB of copies in flight per SM.
   static constexpr int kCtasPerSm = MG <= 4 ? 2 : 1;
-  static constexpr int kStages = MG <= 2 ? 5 : (MG == 4 ? 4 : 6);
+  static constexpr int kStages = MG <= 2 ? 5 : (MG == 4 ? 4 : 6);   // at least 4: units it+2 .. it+S-1 are in flight
   static constexpr int kSmemBytes = kStages * kStageBytes + 128;
   static constexpr int kAccRegs = MG * 2 * 4;            // per lane: token groups x column chunks x 4
   static_assert(kSmemBytes * kCtasPerSm + 1024 * kCtasPerSm <= 233472, "stage rings exceed the shared memory of an SM");
@@ -177,12 +178,28 @@ __device__ __forceinline__ uint32_t w_chunk(uint32_t cc, uint32_t row) { return 
 // of one 16-k block fall into four different bank quarters (one 8-byte load per lane).
 __device__ __forceinline__ uint32_t x_chunk(uint32_t cc, uint32_t tok) { return cc ^ ((tok & 3u) << 1); }
 
+// (a & b) | c in one instruction.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 template <typename T, int MG>
 __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_kernel(const Params p) {
   using C = Cfg<MG>;
   using P16 = Pack16<T>;
   using V2 = typename P16::V2;
   constexpr int S = C::kStages;
+  constexpr int kXChunks = (C::kTokens + 15) / 16;   // activation chunks a thread stages per unit
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_addr(smem_raw) + 127u) & ~127u;
 
@@ -195,16 +212,18 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
   const long long u_begin = run_start(units, ctas, blockIdx.x);
   const long long u_end = run_start(units, ctas, blockIdx.x + 1);
   const int n_units = static_cast<int>(u_end - u_begin);
+  const int tile0 = static_cast<int>(u_begin / p.k_steps);
+  const int step0 = static_cast<int>(u_begin - static_cast<long long>(tile0) * p.k_steps);
 
   // ------------------------------ loader state ------------------------------
   // Every thread copies the same chunks of every unit: 16-byte chunk cc of byte-rows
   // r0, r0 + 16, r0 + 32, r0 + 48 of the packed tile, chunk cc of token rows r0, r0 + 16, ...
   // of the activation slice, and (warps 0 and 1) chunk `lane` of the scale / zero-point row.
   // Source pointers advance by a constant per K-step and are rebuilt when the tile changes.
-  int tile_l = static_cast<int>(u_begin / p.k_steps);
-  int step_l = static_cast<int>(u_begin - static_cast<long long>(tile_l) * p.k_steps);
+  int tile_l = tile0, step_l = step0;
   int grp_l = step_l / p.gs_steps, in_grp_l = step_l - grp_l * p.gs_steps;
   int loaded = 0;
+  uint32_t st_load = ring;                       // stage the next copy goes to
   const uint32_t ld_r0 = tid >> 4, ld_cc = tid & 15u;
   const uint32_t w_dst = ld_r0 * kTileN + (w_chunk(ld_cc, ld_r0) << 4);
   const uint32_t x_dst = kWBytes + ld_r0 * (kStepK * 2) + (x_chunk(ld_cc, ld_r0) << 4);
@@ -215,6 +234,10 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
   const uint8_t* const sz_base = static_cast<const uint8_t*>(warp == 0 ? p.scales : p.zeros);
   const bool sz_active = warp == 0 || (warp == 1 && p.has_zeros);
   const uint32_t sz_dst = kWBytes + C::kXBytes + (warp == 1 ? kTileN * 2 : 0) + (lane << 4);
+  // tokens this thread stages: ld_r0 + 16 i; rows at or beyond M are written as zeros
+  uint32_t x_bytes[kXChunks];
+#pragma unroll
+  for (int i = 0; i < kXChunks; ++i) x_bytes[i] = static_cast<int>(ld_r0) + 16 * i < p.m ? 16u : 0u;
   const uint8_t* w_src;
   const uint8_t* x_src = a_bytes + (static_cast<size_t>(ld_r0) * p.k + ld_cc * 8) * 2 + static_cast<size_t>(step_l) * (kStepK * 2);
   const uint8_t* sz_src;
@@ -231,20 +254,18 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
   enter_tile(tile_l, step_l, grp_l);
   auto issue = [&]() {
     if (loaded < n_units) {
-      const uint32_t st = ring + static_cast<uint32_t>(loaded % S) * C::kStageBytes;
+      // a chunk outside the matrix keeps the (valid) base pointer and copies zero bytes
+      const size_t wr = w_bytes ? w_row16 : 0;
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        cp_async16(st + w_dst + i * (16 * kTileN), w_bytes ? w_src + i * w_row16 : w_src, w_bytes);
+      for (int i = 0; i < 4; ++i) cp_async16(st_load + w_dst + i * (16 * kTileN), w_src + i * wr, w_bytes);
 #pragma unroll
-      for (int i = 0; i < (C::kTokens + 15) / 16; ++i) {
-        const int tok = static_cast<int>(ld_r0) + 16 * i;
-        if (tok < C::kTokens) {
-          const bool ok = tok < p.m;
-          cp_async16(st + x_dst + i * (16 * kStepK * 2), ok ? x_src + i * x_row16 : a_bytes, ok ? 16u : 0u);
-        }
+      for (int i = 0; i < kXChunks; ++i) {
+        if (16 * i + 15 < C::kTokens || static_cast<int>(ld_r0) + 16 * i < C::kTokens)
+          cp_async16(st_load + x_dst + i * (16 * kStepK * 2), x_bytes[i] ? x_src + i * x_row16 : a_bytes, x_bytes[i]);
       }
-      if (sz_active) cp_async16(st + sz_dst, sz_src, sz_bytes);
+      if (sz_active) cp_async16(st_load + sz_dst, sz_src, sz_bytes);
       ++loaded;
+      st_load = (st_load == ring + (S - 1) * C::kStageBytes) ? ring : st_load + C::kStageBytes;
       if (++step_l == p.k_steps) {
         step_l = 0; grp_l = 0; in_grp_l = 0; ++tile_l;
         x_src -= static_cast<size_t>(p.k_steps - 1) * (kStepK * 2);
@@ -260,6 +281,21 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
     }
     cp_async_commit();
   };
+  // The k order inside a 16-k block that the weight fragments imply (slot pairs hold
+  // k = 4s, 4s+2 and 4s+1, 4s+3) is given to the activations once, by the thread that
+  // copied the chunk, in place: [x0 x1 x2 x3] -> [x0 x2 x1 x3] for both 4-k groups of the
+  // chunk. The consumers' 8-byte loads then are the two B-fragment registers as they are.
+  auto permute_x = [&](uint32_t st) {
+#pragma unroll
+    for (int i = 0; i < kXChunks; ++i) {
+      if (16 * i + 15 < C::kTokens || static_cast<int>(ld_r0) + 16 * i < C::kTokens) {
+        const uint32_t addr = st + x_dst + i * (16 * kStepK * 2);
+        const uint4 v = lds128(addr);
+        sts128(addr, make_uint4(__byte_perm(v.x, v.y, 0x5410), __byte_perm(v.x, v.y, 0x7632),
+                                __byte_perm(v.z, v.w, 0x5410), __byte_perm(v.z, v.w, 0x7632)));
+      }
+    }
+  };
 
   // ------------------------------ compute state ------------------------------
   float acc[MG][2][4];
@@ -270,8 +306,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[t][c][j] = 0.f;
 
-  int tile = static_cast<int>(u_begin / p.k_steps);
-  int step = static_cast<int>(u_begin - static_cast<long long>(tile) * p.k_steps);
+  int tile = tile0, step = step0;
   int seg_first_step = step;
   // partial segments of this run (at most two: the head of the run and its tail), published
   // after the main loop
@@ -282,12 +317,15 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
   // (mi / 2) of the pair and column chunk (mi % 2) of this warp; row = lane % 8
   const uint32_t ld_mi = lane >> 3, ld_i = lane & 7u;
   const uint32_t ld_off = (8u * (ld_mi >> 1) + ld_i) * kTileN + (w_chunk(2u * warp + (ld_mi & 1u), ld_i) << 4);
-  // lane's 8 bytes of an activation row: token 8*tg + g, k = 16*kb + 4*s .. +3; all tokens
-  // 8t + g of a lane share g % 4, hence the chunk swizzle
-  const uint32_t x_row_off = kWBytes + static_cast<uint32_t>(g) * (kStepK * 2) + 8u * (s & 1u);
-  const uint32_t x_swz = (static_cast<uint32_t>(g) & 3u) << 1;
+  // lane's 8 bytes of an activation row: token 8*tg + g, k-slots of lane s in K-block kb sit in
+  // chunk (2 kb + s/2) ^ ((g % 4) * 2) = 2 (kb ^ (g % 4)) + s/2; kb ^ (g % 4) = (kb & 4) | ((kb & 3) ^ (g % 4))
+  const uint32_t x_row_off = kWBytes + static_cast<uint32_t>(g) * (kStepK * 2) + 8u * (s & 1u) + 16u * (s >> 1);
+  uint32_t x_kb_off[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) x_kb_off[q] = x_row_off + 32u * (static_cast<uint32_t>(q) ^ (static_cast<uint32_t>(g) & 3u));
   const uint32_t sz_off = kWBytes + C::kXBytes + (32u * warp + 2u * g) * 2u;
   const V2 magic2 = P16::splat(P16::kMagic);
+  const uint32_t kMask = 0x000F000Fu, kMagicBits = P16::kMagic2;
   T* cmat = static_cast<T*>(p.c);
   const T* bias = static_cast<const T*>(p.bias);
   constexpr int kSlotFloats = C::kAccRegs * 32;
@@ -316,16 +354,22 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
     }
   };
 
+  // prologue: S-1 units on their way; the first one's activations in consumer order
 #pragma unroll 1
   for (int i = 0; i < S - 1; ++i) issue();
+  cp_async_wait<S - 2>();
+  permute_x(ring);
+  uint32_t st = ring;            // stage of the unit being computed
+  uint32_t st_next = n_units > 1 ? ring + C::kStageBytes : ring;
 
 #pragma unroll 1
   for (int it = 0; it < n_units; ++it) {
-    cp_async_wait<S - 2>();   // this thread's copies of unit `it` have landed ...
-    __syncthreads();          // ... and everyone's; and everyone has finished reading unit it-1
+    cp_async_wait<S - 3>();   // this thread's copies of units it and it+1 have landed ...
+    __syncthreads();          // ... everyone's of unit it (and its permuted activations) too;
+                              // and everyone has finished reading unit it-1
     issue();                  // refill the stage unit it-1 occupied
+    if (it + 1 < n_units) permute_x(st_next);   // own chunks only: no other thread touches them before the next barrier
 
-    const uint32_t st = ring + static_cast<uint32_t>(it % S) * C::kStageBytes;
     // scales and zero-points of this lane's columns: chunk c, columns 2g and 2g+1
     V2 sc[2][2], zz[2][2];
     uint32_t sraw[2], zraw[2];
@@ -356,28 +400,31 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
         uint32_t b[MG][2];
 #pragma unroll
         for (int t = 0; t < MG; ++t) {
-          const uint2 x = lds64(st + x_row_off + t * (8 * kStepK * 2) + (((2u * kb + (s >> 1)) ^ x_swz) << 4));
-          b[t][0] = __byte_perm(x.x, x.y, 0x5410);   // k = 4s, 4s+2
-          b[t][1] = __byte_perm(x.x, x.y, 0x7632);   // k = 4s+1, 4s+3
+          uint32_t xo;
+          if constexpr (kFast) xo = x_kb_off[kb & 3] + (kb >> 2) * 128;   // kb is a compile-time constant here
+          else xo = x_row_off + 32u * (static_cast<uint32_t>(kb) ^ (static_cast<uint32_t>(g) & 3u));
+          const uint2 x = lds64(st + xo + t * (8 * kStepK * 2));
+          b[t][0] = x.x;   // k = 4s, 4s+2
+          b[t][1] = x.y;   // k = 4s+1, 4s+3
         }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const uint32_t w = r[kbi * 2 + c];
           // bytes of w: (row 2s, n 2g) (row 2s, n 2g+1) (row 2s+1, n 2g) (row 2s+1, n 2g+1);
           // low nibble = even k of the row, high nibble = odd k
-          const uint32_t q[4] = {w & 0x000F000Fu, (w >> 8) & 0x000F000Fu, (w >> 4) & 0x000F000Fu,
-                                 (w >> 12) & 0x000F000Fu};
+          const uint32_t ws[4] = {w, w >> 8, w >> 4, w >> 12};
           uint32_t a[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             if constexpr (kFast) {
-              a[j] = P16::bits(__hmul2(__hsub2(P16::from_bits(q[j] | P16::kMagic2), zz[c][j & 1]), sc[c][j & 1]));
+              a[j] = P16::bits(__hmul2(__hsub2(P16::from_bits(and_or(ws[j], kMask, kMagicBits)), zz[c][j & 1]), sc[c][j & 1]));
             } else {
               // zero-points that are not small integers: the fp32 statement, verbatim
+              const uint32_t q = ws[j] & kMask;
               const uint32_t sh = (j & 1) ? 16u : 0u;
               const float zf = P16::to_float((zraw[c] >> sh) & 0xFFFFu), sf = P16::to_float((sraw[c] >> sh) & 0xFFFFu);
-              a[j] = P16::make(__fmul_rn(__fsub_rn(static_cast<float>(q[j] & 15u), zf), sf),
-                               __fmul_rn(__fsub_rn(static_cast<float>(q[j] >> 16), zf), sf));
+              a[j] = P16::make(__fmul_rn(__fsub_rn(static_cast<float>(q & 15u), zf), sf),
+                               __fmul_rn(__fsub_rn(static_cast<float>(q >> 16), zf), sf));
             }
           }
 #pragma unroll
@@ -419,9 +466,11 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
         for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int j = 0; j < 4; ++j) acc[t][c][j] = 0.f;
+      seg_first_step = (step == p.k_steps - 1) ? 0 : step + 1;
     }
     if (++step == p.k_steps) { step = 0; ++tile; }
-    if (seg_last) seg_first_step = step;
+    st = st_next;
+    st_next = (st_next == ring + (S - 1) * C::kStageBytes) ? ring : st_next + C::kStageBytes;
   }
   cp_async_wait<0>();
 

@@ -89,8 +89,8 @@ def w4a16(a, b_packed, scales, zeros, *, group_size=128, bias=None, **kw):
     return c
 
 
-def moe(a, b, expert_offsets, *, num_experts=None, n, k, a_scale=None, b_scale=None, b_layout="nk",
-        block_n=128, block_k=128, out_dtype=None, **kw):
+def moe(a, b, expert_offsets=None, *, num_experts=None, n, k, a_scale=None, b_scale=None, b_layout="nk",
+        block_n=128, block_k=128, out_dtype=None, masked_m=None, expected_m=None, **kw):
     """Grouped expert GEMM over rows sorted by expert.
 
     Without scales this is the reference's own form (``_registry.py:1040-1046``):
@@ -98,6 +98,16 @@ def moe(a, b, expert_offsets, *, num_experts=None, n, k, a_scale=None, b_scale=N
     the block-scaled FP8 form the reference hands to external providers
     (``_registry.py:1677-1700``): ``b [E,N,K]`` by default, bf16 output."""
     _strip_router_kwargs(kw)
+    if masked_m is not None:
+        # masked layout (``_registry.py:1686-1689``): a [E, max_m, K], out [E, max_m, N];
+        # ``expected_m`` is a tuning hint of the external provider and is not needed here
+        if a_scale is None or b_scale is None:
+            raise ValueError("the masked layout needs a_scale and b_scale")
+        e, max_m = a.shape[0], a.shape[1]
+        out = torch.empty(e, max_m, n, device=a.device, dtype=out_dtype or torch.bfloat16)
+        _moe.grouped_gemm_fp8_blockwise_masked(out, a, b, a_scale, b_scale, masked_m, e, max_m, n, k,
+                                               block_n=block_n, block_k=block_k, b_layout=b_layout)
+        return out
     if num_experts is None:
         num_experts = expert_offsets.shape[0] - 1
     total_rows = a.shape[0]

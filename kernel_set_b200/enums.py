@@ -33,3 +33,10 @@ class MemcpyKind(IntEnum):
     HOST_TO_DEVICE = 0
     DEVICE_TO_HOST = 1
     DEVICE_TO_DEVICE = 2
+
+
+class QuantMode(IntEnum):
+    PER_TENSOR = 0
+    PER_TOKEN = 1
+    PER_CHANNEL = 2
+    GROUPWISE = 3

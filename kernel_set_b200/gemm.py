@@ -1,6 +1,7 @@
 """Out-parameter wrappers of the quantized GEMM entry points; signatures of
 ``bindings/python/kernel_set/gemm.py`` of the reference project
-(``gemm_w4a16`` ``:196-225``, ``gemm_fp8_blockwise`` ``:313-362``)."""
+(``gemm_w8a8`` ``:151-193``, ``gemm_w4a16`` ``:196-225``, ``gemm_fp8`` ``:228-280``,
+``gemm_fp8_blockwise`` ``:313-362``)."""
 from __future__ import annotations
 
 from typing import Optional
@@ -9,6 +10,44 @@ import torch
 
 from ._lib import check, lib
 from ._tensor import TensorLike, default_stream, dtype_to_ks, f32_ptr, infer_dtype, ptr
+from .enums import QuantMode
+
+
+def _out_dtype(out, out_dtype, name):
+    if out_dtype is not None:
+        return int(out_dtype)
+    if isinstance(out, torch.Tensor):
+        return int(dtype_to_ks(out.dtype))
+    raise ValueError(f"out_dtype is required for {name}")
+
+
+def gemm_w8a8(c: TensorLike, a_i8: TensorLike, b_i8: TensorLike, a_scale: TensorLike, b_scale: TensorLike,
+              m: int, n: int, k: int, bias: TensorLike = None, a_mode: int = QuantMode.PER_TOKEN,
+              b_mode: int = QuantMode.PER_CHANNEL, out_dtype: int = None, stream: TensorLike = None) -> TensorLike:
+    """W8A8 GEMM: int8 ``A [M,K]`` x int8 ``B [K,N]`` -> ``C [M,N]``;
+    ``a_scale`` / ``b_scale`` fp32 ``[M]`` / ``[N]`` (or ``[1]``); ``bias [N]`` in
+    the output dtype or ``None``."""
+    odt = _out_dtype(c, out_dtype, "ks_gemm_w8a8")
+    check(lib.ks_gemm_w8a8(ptr(c, name="c"), ptr(a_i8, name="a_i8"),
+                           ptr(b_i8, name="b_i8"), f32_ptr(a_scale, name="a_scale"),
+                           f32_ptr(b_scale, name="b_scale"), ptr(bias, name="bias"), int(m), int(n), int(k),
+                           int(a_mode), int(b_mode), odt, default_stream(stream, a_i8)), "ks_gemm_w8a8")
+    return c
+
+
+def gemm_fp8(out: TensorLike, a_fp8: TensorLike, b_fp8: TensorLike, a_scale: TensorLike, b_scale: TensorLike,
+             m: int, n: int, k: int, a_mode: int = QuantMode.PER_TOKEN, b_mode: int = QuantMode.PER_CHANNEL,
+             fp8_dtype: int = None, out_dtype: int = None, stream: TensorLike = None) -> TensorLike:
+    """FP8 GEMM ``C = (a_scale (x) b_scale) * (A_fp8 @ B_fp8)``: ``A [M,K]``,
+    ``B [K,N]`` row-major, scales fp32 ``[M]`` / ``[N]`` (or ``[1]``)."""
+    if fp8_dtype is None:
+        fp8_dtype = infer_dtype(a_fp8, None)
+    odt = _out_dtype(out, out_dtype, "ks_gemm_fp8")
+    check(lib.ks_gemm_fp8(ptr(out, name="out"), ptr(a_fp8, name="a_fp8"), ptr(b_fp8, name="b_fp8"),
+                          f32_ptr(a_scale, name="a_scale"), f32_ptr(b_scale, name="b_scale"), int(m), int(n), int(k),
+                          int(a_mode), int(b_mode), int(fp8_dtype), odt, default_stream(stream, a_fp8)),
+          "ks_gemm_fp8")
+    return out
 
 
 def gemm_w4a16(c: TensorLike, a: TensorLike, b_packed: TensorLike, scales: TensorLike, zeros: TensorLike,

@@ -114,3 +114,27 @@ def unpermute(out: TensorLike, permuted: TensorLike, sorted_token_ids: TensorLik
                                f32_ptr(routing_weights, name="routing_weights"), int(num_tokens), int(top_k),
                                int(hidden), dt, default_stream(stream, permuted)), "ks_moe_unpermute")
     return out
+
+
+def grouped_gemm_fp8_blockwise_masked(out: TensorLike, a_fp8: TensorLike, b_fp8: TensorLike, a_scale: TensorLike,
+                                      b_scale: TensorLike, masked_m: TensorLike, num_experts: int, max_m: int,
+                                      n: int, k: int, block_n: int = 128, block_k: int = 128, b_layout: str = "nk",
+                                      fp8_dtype: Optional[int] = None, out_dtype: Optional[int] = None,
+                                      stream: TensorLike = None) -> TensorLike:
+    """The block-scaled grouped GEMM over the masked layout: ``a_fp8 [E, max_m,
+    K]``, ``masked_m [E]`` int32 (device), ``out [E, max_m, N]``; expert ``e``
+    computes its first ``masked_m[e]`` rows."""
+    if fp8_dtype is None:
+        fp8_dtype = infer_dtype(a_fp8, None)
+    if out_dtype is None:
+        if not isinstance(out, torch.Tensor):
+            raise ValueError("out_dtype is required for raw-pointer outputs")
+        out_dtype = dtype_to_ks(out.dtype)
+    if b_layout not in ("kn", "nk"):
+        raise ValueError("b_layout must be 'kn' or 'nk'")
+    check(lib.ks_moe_grouped_gemm_fp8_blockwise_masked(
+        ptr(out, name="out"), ptr(a_fp8, name="a_fp8"), ptr(b_fp8, name="b_fp8"),
+        f32_ptr(a_scale, name="a_scale"), f32_ptr(b_scale, name="b_scale"), i32_ptr(masked_m, name="masked_m"),
+        int(num_experts), int(max_m), int(n), int(k), int(block_n), int(block_k), 1 if b_layout == "nk" else 0,
+        int(fp8_dtype), int(out_dtype), default_stream(stream, a_fp8)), "ks_moe_grouped_gemm_fp8_blockwise_masked")
+    return out

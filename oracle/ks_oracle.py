@@ -232,6 +232,25 @@ def grouped_gemm_fp8_blockwise(a8, b8, a_scale, b_scale, expert_offsets: Sequenc
     return ref
 
 
+def gemm_fp8_scaled(a8, b8_kn, a_scale, b_scale, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``(acc * a_scale) * b_scale`` with ``acc = A8.float() @ B8.float()``; scales
+    ``[M]`` / ``[N]`` or one element (include/kernel_set/gemm.h:60-77,
+    kernels/src/gemm/gemm_fp8.cu:147-153). ``out_dtype=None`` returns fp32."""
+    acc = a8.float() @ b8_kn.float()
+    ref = (acc * a_scale.float().reshape(-1, 1)) * b_scale.float().reshape(1, -1)
+    return ref if out_dtype is None else ref.to(out_dtype)
+
+
+def gemm_w8a8(a_i8, b_i8, a_scale, b_scale, bias=None, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """Exact integer product (in float64, as bench.py:1228-1232 does), then
+    ``acc * a_scale * b_scale`` (+ bias) in fp32 (kernels/src/gemm/gemm_w8a8.cu:134-141)."""
+    acc = (a_i8.double() @ b_i8.double()).float()
+    ref = acc * a_scale.float().reshape(-1, 1) * b_scale.float().reshape(1, -1)
+    if bias is not None:
+        ref = ref + bias.float()
+    return ref if out_dtype is None else ref.to(out_dtype)
+
+
 def moe_route(logits: torch.Tensor, top_k: int):
     """softmax -> top-k -> renormalise (bench.py:1555-1557). Returns (weights
     fp32 [T,k], expert ids int64 [T,k])."""
