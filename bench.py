@@ -479,7 +479,7 @@ def run_cfg5(args, torch, dist, ks, parallel, dev, rank, world):
             gathered.append(torch.cat([p[:, :int(w)] for p, w in zip(parts, widths)], dim=1).cpu())
         else:
             gathered.append(t.cpu())
-    parity = None
+    parity, ref32 = None, None
     if rank == 0:
         a8w, asw, w8w, wsw = gathered
         ref32 = orc.fp8_gemm_blockwise(a8w.view(torch.float8_e4m3fn), w8w.view(torch.float8_e4m3fn), asw, wsw, 128, 128,
@@ -487,7 +487,7 @@ def run_cfg5(args, torch, dist, ks, parallel, dev, rank, world):
         got = out[:win, :win].float().cpu()
         err_ulp = ((got - ref32).abs() / orc.bf16_ulp(ref32).float())
         parity = {"window": f"rows 0..{win}, columns 0..{win} of the all-reduced output vs the oracle on unsplit K",
-                  "rel_frobenius": orc.rel_frobenius(got, ref32),
+                  "rel_frobenius": orc.rel_frobenius(got, ref32.to(torch.bfloat16).float()),
                   "max_err_bf16_ulp": float(err_ulp.max()), "frac_above_2_ulp": float((err_ulp > 2).float().mean()),
                   "note": "bf16 partials are rounded once per rank before the sum and once after"}
 
@@ -496,6 +496,32 @@ def run_cfg5(args, torch, dist, ks, parallel, dev, rank, world):
     ms_quant = timed(quant, steps, 1, barrier, torch)
     ms_gemm = timed(gemm, steps, 1, barrier, torch)
     ms_red = timed(reduce, steps, 1, barrier, torch) if world > 1 else 0.0
+
+    # the same step with fp32 partials: twice the bytes on NVLink, one rounding in all
+    fp32 = None
+    if world > 1:
+        out32 = torch.empty(m5, n5, dtype=torch.float32, device=dev)
+
+        def step32():
+            quant()
+            ks.gemm.gemm_fp8_blockwise(out32, a8, w8, a_s, ws, m5, n5, hi - lo, b_layout="nk")
+            dist.all_reduce(out32)
+
+        step32()
+        barrier()
+        par32 = None
+        if rank == 0:
+            got32 = out32[:win, :win].to(torch.bfloat16).float().cpu()
+            e32 = ((got32 - ref32).abs() / orc.bf16_ulp(ref32).float())
+            par32 = {"rel_frobenius": orc.rel_frobenius(got32, ref32.to(torch.bfloat16).float()),
+                     "max_err_bf16_ulp": float(e32.max()), "frac_above_2_ulp": float((e32 > 2).float().mean())}
+        ms_step32 = timed(step32, steps, 1, barrier, torch)
+        ms_red32 = timed(lambda: dist.all_reduce(out32), steps, 1, barrier, torch)
+        t32 = torch.tensor([ms_step32, ms_red32], dtype=torch.float64, device=dev)
+        dist.all_reduce(t32, op=dist.ReduceOp.MAX)
+        fp32 = {"ms_per_step": float(t32[0]), "allreduce_us": float(t32[1]) * 1e3,
+                "value": 2.0 * m5 * n5 * k5 / (float(t32[0]) * 1e-3) / 1e12, "parity": par32}
+        del out32
     t = torch.tensor([ms_step, ms_quant, ms_gemm, ms_red], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -512,7 +538,7 @@ def run_cfg5(args, torch, dist, ks, parallel, dev, rank, world):
         "gemm_us": ms_gemm * 1e3, "quantizer_us": ms_quant * 1e3, "allreduce_us": ms_red * 1e3,
         "gemm_tflops_per_gpu": flops / world / (ms_gemm * 1e-3) / 1e12,
         "allreduce_busbw_gbs": (ring_bytes / (ms_red * 1e-3) / 1e9) if world > 1 else None,
-        "parity": parity}
+        "parity": parity, "fp32_partials": fp32}
 
 
 def moe_small_parity(torch, dist, ks, parallel, dev, rank, world):

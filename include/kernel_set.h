@@ -7,4 +7,5 @@
 #include "kernel_set/quant.h"
 #include "kernel_set/moe.h"
 #include "kernel_set/activation.h"
+#include "kernel_set/norm.h"
 #endif /* KERNEL_SET_H_ */

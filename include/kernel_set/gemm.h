@@ -154,6 +154,29 @@ KS_API ks_status_t ks_gemm_fp8_blockwise_nt(void* out, const void* a_fp8,
                                             ks_dtype_t out_dtype,
                                             ks_stream_t stream);
 
+/*
+ * The block-scaled GEMM (128 x 128 weight blocks, 1 x 128 activation groups)
+ * with the activation scales stored column-major, as
+ * ks_quantize_fp8_group_colscale writes them:
+ *   a_scale_t[kb * a_scale_ld + m]
+ * b_layout 0: b_fp8 [K,N], b_scale [ceil(K/128), ceil(N/128)];
+ * b_layout 1: b_fp8 [N,K], b_scale [ceil(N/128), ceil(K/128)].
+ * The epilogue's scale loads of a warp then touch one 128-byte line per
+ * K-block instead of 32. Only the tcgen05 kernel serves this entry (K, and N
+ * for [K,N], multiples of 16; UNSUPPORTED_SHAPE otherwise). No counterpart in
+ * the reference.
+ */
+KS_API ks_status_t ks_gemm_fp8_blockwise_colscale(void* out, const void* a_fp8,
+                                                  const void* b_fp8,
+                                                  const float* a_scale_t,
+                                                  int64_t a_scale_ld,
+                                                  const float* b_scale,
+                                                  int64_t m, int64_t n,
+                                                  int64_t k, int b_layout,
+                                                  ks_dtype_t fp8_dtype,
+                                                  ks_dtype_t out_dtype,
+                                                  ks_stream_t stream);
+
 KS_END_EXTERN_C
 
 #endif /* KERNEL_SET_GEMM_H_ */

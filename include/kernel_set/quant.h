@@ -60,6 +60,24 @@ KS_API ks_status_t ks_repack_int4(void* out_packed, const void* qweight,
                                   int64_t size_n, int num_bits,
                                   ks_stream_t stream);
 
+/*
+ * ks_quantize_fp8_group(group_size = 128) with the scales stored column-major:
+ *   scale_t[g * scale_ld + r] = scale of row r, group g   (scale_ld >= rows)
+ * so that the rows of a GEMM tile find their scales of one K-block contiguous
+ * (one 512-byte run per 128 rows, TMA-loadable when scale_ld is a multiple of
+ * 4); ks_gemm_fp8_blockwise_colscale consumes this layout. Codes and scale
+ * values are those of ks_quantize_fp8_group. cols must be a multiple of 128.
+ * No counterpart in the reference's C ABI (its external providers offer the
+ * layout as an option of their own quantizer).
+ */
+KS_API ks_status_t ks_quantize_fp8_group_colscale(void* out, float* scale_t,
+                                                  int64_t scale_ld,
+                                                  const void* input,
+                                                  int64_t rows, int64_t cols,
+                                                  ks_dtype_t in_dtype,
+                                                  ks_dtype_t fp8_dtype,
+                                                  ks_stream_t stream);
+
 KS_END_EXTERN_C
 
 #endif /* KERNEL_SET_QUANT_H_ */

@@ -164,11 +164,14 @@ _FP8_BW = [_VP, _VP, _VP, POINTER(c_float), POINTER(c_float), c_int64, c_int64, 
 _SCALED = [_VP, _VP, _VP, POINTER(c_float), POINTER(c_float)]
 _decl("ks_gemm_fp8", _SCALED + [c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, _VP])
 _decl("ks_gemm_w8a8", _SCALED + [_VP, c_int64, c_int64, c_int64, c_int, c_int, c_int, _VP])
+_decl("ks_gemm_fp8_blockwise_colscale", [_VP, _VP, _VP, POINTER(c_float), c_int64, POINTER(c_float), c_int64, c_int64,
+                                        c_int64, c_int, c_int, c_int, _VP])
 _decl("ks_gemm_fp8_blockwise", _FP8_BW)
 _decl("ks_gemm_fp8_blockwise_nt", _FP8_BW)
 
 # quant.h
 _decl("ks_quantize_fp8_group", [_VP, POINTER(c_float), _VP, c_int64, c_int64, c_int, c_int, c_int, _VP])
+_decl("ks_quantize_fp8_group_colscale", [_VP, POINTER(c_float), c_int64, _VP, c_int64, c_int64, c_int, c_int, _VP])
 _decl("ks_dequantize_int4", [_VP, _VP, _VP, _VP, c_int64, c_int64, c_int, c_int, _VP])
 _decl("ks_repack_int4", [_VP, _VP, _VP, c_int64, c_int64, c_int, _VP])
 
@@ -182,6 +185,10 @@ _decl("ks_moe_grouped_gemm", [_VP, _VP, _VP, POINTER(c_int32), c_int, c_int64, c
 _decl("ks_moe_grouped_gemm_fp8_blockwise",
       [_VP, _VP, _VP, POINTER(c_float), POINTER(c_float), POINTER(c_int32), c_int, c_int64, c_int64, c_int64,
        c_int, c_int, c_int, c_int, c_int, _VP])
+
+# norm.h
+_decl("ks_rms_norm", [_VP, _VP, _VP, c_int64, c_int64, c_float, c_int, _VP])
+_decl("ks_rms_norm_quant_fp8", [_VP, POINTER(c_float), _VP, _VP, c_int64, c_int64, c_float, c_int, c_int, _VP])
 
 # activation.h
 _decl("ks_swiglu", [_VP, _VP, _VP, c_int64, c_int64, c_int, _VP])

@@ -206,4 +206,33 @@ ks_status_t ks_moe_grouped_gemm_fp8_blockwise_masked(void* out, const void* a_fp
   return sm100::launch_fp8_blockwise(a, as_stream(stream));
 }
 
+ks_status_t ks_gemm_fp8_blockwise_colscale(void* out, const void* a_fp8, const void* b_fp8, const float* a_scale_t,
+                                           int64_t a_scale_ld, const float* b_scale, int64_t m, int64_t n,
+                                           int64_t k, int b_layout, ks_dtype_t fp8_dtype, ks_dtype_t out_dtype,
+                                           ks_stream_t stream) {
+  using namespace ksb;
+  const char* where = "ks_gemm_fp8_blockwise_colscale";
+  if (b_layout != 0 && b_layout != 1)
+    KSB_FAIL(KS_ERROR_INVALID_ARGUMENT, std::string(where) + ": b_layout must be 0 ([K,N]) or 1 ([N,K])");
+  ks_status_t st = check_common(where, out, a_fp8, b_fp8, a_scale_t, b_scale, m, n, k, 128, 128, fp8_dtype, out_dtype,
+                                false);
+  if (st != KS_SUCCESS) return st;
+  if (a_scale_ld < m) KSB_FAIL(KS_ERROR_INVALID_ARGUMENT, std::string(where) + ": a_scale_ld must be at least m");
+  st = require_sm100(where);
+  if (st != KS_SUCCESS) return st;
+  st = poll_kernel_fault(where);
+  if (st != KS_SUCCESS) return st;
+  sm100::Fp8GemmArgs a;
+  a.where = where; a.out = out; a.a = a_fp8; a.b = b_fp8; a.a_scale = a_scale_t; a.a_scale_ld = a_scale_ld;
+  a.b_scale = b_scale; a.m = m; a.n = n; a.k = k; a.nt = b_layout == 1;
+  a.e5m2 = fp8_dtype == KS_DTYPE_F8E5M2; a.out_dtype = out_dtype;
+  const EnvChoice env = env_choice();
+  a.force_bn = env.bn;
+  a.force_split = env.split;
+  if (!sm100::fp8_blockwise_eligible(a))
+    KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE,
+             std::string(where) + ": needs K (and N for [K,N]) multiples of 16 and 16-byte aligned operands");
+  return sm100::launch_fp8_blockwise(a, as_stream(stream));
+}
+
 }  // extern "C"

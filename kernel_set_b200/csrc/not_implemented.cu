@@ -73,7 +73,6 @@ KSB_NOT_IMPLEMENTED(ks_moe_gate_sigmoid_group_topk)
 KSB_NOT_IMPLEMENTED(ks_fused_rmsnorm_gated)
 KSB_NOT_IMPLEMENTED(ks_layer_norm)
 KSB_NOT_IMPLEMENTED(ks_layer_norm_backward)
-KSB_NOT_IMPLEMENTED(ks_rms_norm)
 KSB_NOT_IMPLEMENTED(ks_rms_norm_backward)
 KSB_NOT_IMPLEMENTED(ks_rms_norm_residual)
 

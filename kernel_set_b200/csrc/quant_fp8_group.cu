@@ -43,6 +43,32 @@ int quant_stream_blocks_per_sm() {
 // A thread owns kSegs segments, all loaded before the first is used. Measured on B200 for
 // [4096, 7168] bf16: 22 us with one segment per thread, 25 us with two, 35 us with four
 // (fewer resident threads cost more than the extra loads in flight gain), so one it is.
+// Column-major scales: scale_t[g * ld + row] instead of scale[row * groups + g], so that the
+// 128 rows of a GEMM tile find their scales of one K-block in 512 contiguous bytes.
+template <typename T, bool E5M2>
+__global__ void __launch_bounds__(256)
+quant_group128_colscale_kernel(uint8_t* __restrict__ out, float* __restrict__ scale_t, int64_t ld,
+                               const T* __restrict__ in, int64_t total_groups, int groups_per_row, float qmax) {
+  const int64_t seg = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const bool live = (seg >> 3) < total_groups;
+  float v[16];
+  if (live) {
+    Vec16<T>::load(in + seg * 16, v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+  }
+  float sc;
+  const uint4 codes = quant_segment_codes<E5M2>(v, qmax, &sc);
+  if (!live) return;
+  if ((threadIdx.x & 7) == 0) {
+    const int64_t grp = seg >> 3;
+    const int64_t row = grp / groups_per_row;
+    scale_t[(grp - row * groups_per_row) * ld + row] = sc;
+  }
+  __stcs(reinterpret_cast<uint4*>(out + seg * 16), codes);
+}
+
 template <typename T, bool E5M2, int kSegs>
 __global__ void __launch_bounds__(256)
 quant_group128_kernel(uint8_t* __restrict__ out, float* __restrict__ scale,
@@ -175,5 +201,45 @@ extern "C" ks_status_t ks_quantize_fp8_group(void* out, float* scale, const void
   else KSB_Q(__nv_bfloat16);
 #undef KSB_Q
   KSB_CHECK_LAUNCH("ks_quantize_fp8_group");
+  return KS_SUCCESS;
+}
+
+extern "C" ks_status_t ks_quantize_fp8_group_colscale(void* out, float* scale_t, int64_t scale_ld, const void* input,
+                                                      int64_t rows, int64_t cols, ks_dtype_t in_dtype,
+                                                      ks_dtype_t fp8_dtype, ks_stream_t stream) {
+  using namespace ksb;
+  const char* where = "ks_quantize_fp8_group_colscale";
+  KSB_REQUIRE_PTR(out);
+  KSB_REQUIRE_PTR(scale_t);
+  KSB_REQUIRE_PTR(input);
+  if (rows <= 0 || cols <= 0) KSB_FAIL(KS_ERROR_INVALID_ARGUMENT, "ks_quantize_fp8_group_colscale: bad shape");
+  if (scale_ld < rows) KSB_FAIL(KS_ERROR_INVALID_ARGUMENT, "ks_quantize_fp8_group_colscale: scale_ld must be at least rows");
+  if (cols % 128 != 0 || !aligned16(input) || !aligned16(out))
+    KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE,
+             "ks_quantize_fp8_group_colscale: cols must be a multiple of 128 and the buffers 16-byte aligned");
+  if (!is_fp8(fp8_dtype)) KSB_FAIL(KS_ERROR_UNSUPPORTED_DTYPE, "ks_quantize_fp8_group_colscale: fp8_dtype must be e4m3 or e5m2");
+  if (!is_float3(in_dtype)) KSB_FAIL(KS_ERROR_UNSUPPORTED_DTYPE, "ks_quantize_fp8_group_colscale: unsupported dtype");
+  const int64_t groups_per_row = cols / 128;
+  if (rows > (INT64_C(1) << 31) / groups_per_row * 4)
+    KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE, "ks_quantize_fp8_group_colscale: grid exceeds CUDA grid limits");
+  ks_status_t st = require_sm100(where);
+  if (st != KS_SUCCESS) return st;
+  cudaStream_t s = as_stream(stream);
+  const int64_t total_groups = rows * groups_per_row;
+  const unsigned blocks = static_cast<unsigned>((total_groups * 8 + 255) / 256);
+  uint8_t* o = static_cast<uint8_t*>(out);
+  const bool e5 = fp8_dtype == KS_DTYPE_F8E5M2;
+#define KSB_QC(T)                                                                                                   \
+  do {                                                                                                              \
+    if (e5) quant_group128_colscale_kernel<T, true><<<blocks, 256, 0, s>>>(o, scale_t, scale_ld, static_cast<const T*>(input), \
+                                                                           total_groups, static_cast<int>(groups_per_row), 57344.0f); \
+    else quant_group128_colscale_kernel<T, false><<<blocks, 256, 0, s>>>(o, scale_t, scale_ld, static_cast<const T*>(input),  \
+                                                                         total_groups, static_cast<int>(groups_per_row), 448.0f);  \
+  } while (0)
+  if (in_dtype == KS_DTYPE_F32) KSB_QC(float);
+  else if (in_dtype == KS_DTYPE_F16) KSB_QC(__half);
+  else KSB_QC(__nv_bfloat16);
+#undef KSB_QC
+  KSB_CHECK_LAUNCH(where);
   return KS_SUCCESS;
 }

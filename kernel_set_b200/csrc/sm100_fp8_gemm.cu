@@ -137,6 +137,7 @@ struct Params {
   int split_s;            // 1 = no split
   float4* split_slots;    // [tail tile][part][epilogue warp][16-byte column chunk][lane]
   // MODE 1 / 2 (one scale per row and per column, the whole K range accumulated in TMEM)
+  int64_t as_row_stride, as_kb_stride;   // a_scale[row * as_row_stride + kb * as_kb_stride]
   const void* bias;       // [N] in the output type or NULL
   int a_per_row;          // a_scale is [M] (else one value)
   int b_per_col;          // b_scale is [N] (else one value)
@@ -404,7 +405,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
       const int col0 = tc.n0 + slice * EC;
       int nb = col0 >> 7;
       if (nb > p.nnb - 1) nb = p.nnb - 1;
-      const float* as_ptr = p.a_scale + static_cast<size_t>(row_ok ? row : 0) * p.nkb;
+      const float* as_ptr = p.a_scale + static_cast<size_t>(row_ok ? row : 0) * p.as_row_stride;
       const float* bs_ptr = p.b_scale + static_cast<size_t>(tc.expert) * p.nkb * p.nnb +
                             (NT ? static_cast<size_t>(nb) * p.nkb : static_cast<size_t>(nb));
       const size_t bs_step = NT ? 1 : static_cast<size_t>(p.nnb);
@@ -459,7 +460,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
         for (int j = 0; j < G; ++j) {
           const int kb = kb0 + j;
           const bool in = kb < tc.kb1;
-          as_nxt[j] = (in && row_ok) ? __ldg(as_ptr + kb) : 0.f;
+          as_nxt[j] = (in && row_ok) ? __ldg(as_ptr + kb * p.as_kb_stride) : 0.f;
           bs_nxt[j] = in ? __ldg(bs_ptr + static_cast<size_t>(kb) * bs_step) : 0.f;
         }
       };
@@ -779,6 +780,8 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
   p.a_scale = a.a_scale;
   p.b_scale = a.b_scale;
   p.offsets = a.offsets;
+  p.as_row_stride = a.a_scale_ld > 0 ? 1 : (a.k + kBK - 1) / kBK;
+  p.as_kb_stride = a.a_scale_ld > 0 ? a.a_scale_ld : 1;
   p.masked_m = a.masked_m;
   p.max_m = static_cast<int>(a.max_m);
   p.bias = a.bias;

@@ -14,7 +14,9 @@ struct Fp8GemmArgs {
   void* out = nullptr;             // [m, n] out_dtype
   const void* a = nullptr;         // [m, k] fp8
   const void* b = nullptr;         // nt: [E][n, k]; else [E][k, n]
-  const float* a_scale = nullptr;  // [m, ceil(k/128)]
+  const float* a_scale = nullptr;  // [m, ceil(k/128)]; or, with a_scale_ld > 0, stored column-major:
+                                   // a_scale[kb * a_scale_ld + row]
+  int64_t a_scale_ld = 0;
   const float* b_scale = nullptr;  // nt: [E][ceil(n/128), ceil(k/128)]; else transposed
   const int32_t* offsets = nullptr;  // [E+1] row boundaries; NULL = one dense problem
   int num_experts = 1;

@@ -103,3 +103,25 @@ def gemm_fp8_blockwise(out: TensorLike, a_fp8: TensorLike, b_fp8: TensorLike, a_
              int(m), int(n), int(k), int(block_n), int(block_k), int(fp8_dtype), int(out_dtype),
              default_stream(stream, out if not isinstance(out, int) else a_fp8)), name)
     return out
+
+
+def gemm_fp8_blockwise_colscale(out: TensorLike, a_fp8: TensorLike, b_fp8: TensorLike, a_scale_t: TensorLike,
+                                b_scale: TensorLike, m: int, n: int, k: int, a_scale_ld: Optional[int] = None,
+                                fp8_dtype: int = None, out_dtype: int = None, stream: TensorLike = None,
+                                b_layout: str = "kn") -> TensorLike:
+    """The block-scaled GEMM with column-major activation scales ``a_scale_t
+    [ceil(K/128), a_scale_ld]`` as ``quant.quantize_fp8_group_colscale`` writes
+    them; everything else as :func:`gemm_fp8_blockwise`."""
+    if fp8_dtype is None:
+        fp8_dtype = infer_dtype(a_fp8, None)
+    odt = _out_dtype(out, out_dtype, "ks_gemm_fp8_blockwise_colscale")
+    if b_layout not in ("kn", "nk"):
+        raise ValueError("b_layout must be 'kn' or 'nk'")
+    if a_scale_ld is None:
+        a_scale_ld = a_scale_t.shape[-1]
+    check(lib.ks_gemm_fp8_blockwise_colscale(ptr(out, name="out"), ptr(a_fp8, name="a_fp8"), ptr(b_fp8, name="b_fp8"),
+                                             f32_ptr(a_scale_t, name="a_scale_t"), int(a_scale_ld),
+                                             f32_ptr(b_scale, name="b_scale"), int(m), int(n), int(k),
+                                             1 if b_layout == "nk" else 0, int(fp8_dtype), odt,
+                                             default_stream(stream, a_fp8)), "ks_gemm_fp8_blockwise_colscale")
+    return out

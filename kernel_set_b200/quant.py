@@ -23,6 +23,22 @@ def quantize_fp8_group(out: TensorLike, scale: TensorLike, input: TensorLike, ro
     return out, scale
 
 
+def quantize_fp8_group_colscale(out: TensorLike, scale_t: TensorLike, input: TensorLike, rows: int, cols: int,
+                                scale_ld: Optional[int] = None, in_dtype: Optional[int] = None,
+                                fp8_dtype: int = DType.F8E4M3, stream: TensorLike = None):
+    """1 x 128 FP8 quantization with the scales stored column-major:
+    ``scale_t [cols/128, scale_ld]`` fp32, ``scale_t[g, r]`` = scale of row ``r``,
+    group ``g`` (``scale_ld >= rows``; default: ``scale_t``'s row length).
+    Returns ``(out, scale_t)``."""
+    dt = infer_dtype(input, in_dtype)
+    if scale_ld is None:
+        scale_ld = scale_t.shape[-1]
+    check(lib.ks_quantize_fp8_group_colscale(ptr(out, name="out"), f32_ptr(scale_t, name="scale_t"), int(scale_ld),
+                                             ptr(input, name="input"), int(rows), int(cols), dt, int(fp8_dtype),
+                                             default_stream(stream, input)), "ks_quantize_fp8_group_colscale")
+    return out, scale_t
+
+
 def dequantize_int4(out: TensorLike, qweight_packed: TensorLike, scales: TensorLike, zeros: TensorLike,
                     k: int, n: int, group_size: int, out_dtype: Optional[int] = None,
                     stream: TensorLike = None) -> TensorLike:

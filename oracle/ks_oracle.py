@@ -270,6 +270,12 @@ def sort_by_expert(expert_ids: torch.Tensor, num_experts: int):
     return order, offsets
 
 
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """``(x * rsqrt(mean(x^2) + eps)).to(dtype) * weight`` (bench.py:877-879)."""
+    f = x.float()
+    return (f * torch.rsqrt(f.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
+
+
 def moe_permute(x: torch.Tensor, sorted_token_ids: torch.Tensor, top_k: int) -> torch.Tensor:
     """Gather rows by the permutation: row r of the result is token
     ``sorted_token_ids[r] // top_k`` (bench.py:2546-2548)."""

@@ -33,7 +33,7 @@ def test_headers_compile_as_c_and_cpp(tmp_path):
 
 def test_every_declared_symbol_is_exported(ks):
     decl = declared_symbols()
-    assert len(decl) == 37, decl
+    assert len(decl) == 41, decl
     out = subprocess.run(["nm", "-D", "--defined-only", ks.LIB_PATH], capture_output=True, text=True, check=True)
     exported = sorted(l.split()[-1] for l in out.stdout.splitlines() if " T " in l)
     assert [s for s in decl if s not in exported] == []
@@ -56,7 +56,7 @@ def test_every_reference_symbol_resolves(ks):
             assert fn() == ks.Status.NOT_IMPLEMENTED, name
             assert name in ks.runtime.last_error_string()
     implemented = sorted(n for _, n in rows if n in ours)
-    assert len(implemented) == 31 and "ks_moe_unpermute" in implemented and "ks_swiglu_packed" in implemented
+    assert len(implemented) == 32 and "ks_moe_unpermute" in implemented and "ks_swiglu_packed" in implemented
 
 
 def test_introspection(ks):

@@ -42,3 +42,67 @@ def test_moe_layer_on_device(ks, cuda):
     torch.cuda.synchronize()
     ks.runtime.stream_synchronize(0)
     assert orc.rel_frobenius(got.cpu().float(), ref.float()) < 4e-3
+
+
+def _nccl_worker(rank, world, port, q):
+    import os
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    for p in (os.path.dirname(here), os.path.join(os.path.dirname(here), "oracle"), here):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from test_parallel_cpu import dense_moe_reference
+        # row-parallel linear: K split over the ranks, bf16 partials all-reduced over NCCL
+        x, w8, ws = make_linear(64, 512, 2048, 2)
+        lo, hi = par.block_range(2048, rank, world)
+        a8, a_s = orc.quantize_fp8_group(x, 128)
+        _, _, b_sh, bs_sh, _ = par.shard_k(a8, a_s, w8, ws, rank, world, "nk")
+        out = par.row_parallel_linear(x[:, lo:hi].contiguous().to(dev), b_sh.to(dev), bs_sh.to(dev))
+        torch.cuda.synchronize()
+        full32 = orc.fp8_gemm_blockwise(a8, w8, a_s, ws, layout="nk", out_dtype=None)
+        frob_row = orc.rel_frobenius(out.float().cpu(), full32)
+        # expert-parallel MoE: tokens and experts both split, fp8 rows through all_to_all
+        xm, ids, w, w1, s1, w2, s2 = make_moe(64, 256, 128, 8, 2, 3)
+        t = 64 // world
+        t_lo, t_hi = rank * t, (rank + 1) * t
+        e_lo, e_hi = par.expert_range(8, rank, world)
+        got = par.expert_parallel_moe(xm[t_lo:t_hi].to(dev), ids[t_lo:t_hi].to(dev), w[t_lo:t_hi].to(dev),
+                                      w1[e_lo:e_hi].to(dev), s1[e_lo:e_hi].to(dev), w2[e_lo:e_hi].to(dev),
+                                      s2[e_lo:e_hi].to(dev), 8)
+        torch.cuda.synchronize()
+        ref = dense_moe_reference(xm, ids, w, w1, s1, w2, s2)[t_lo:t_hi]
+        frob_moe = orc.rel_frobenius(got.float().cpu(), ref.float())
+        q.put((rank, float(frob_row), float(frob_moe)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_nccl_world2_row_parallel_and_expert_parallel(ks, cuda):
+    """Two ranks on two GPUs over NCCL: the all-reduce of the row-parallel linear and the
+    all-to-all dispatch / combine of the expert-parallel layer against the oracle on the
+    unsplit problem. Needs two devices; a one-GPU machine skips it."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from test_parallel_cpu import _free_port
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=300) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, frob_row, frob_moe in results:
+        # two bf16 partials rounded before the sum and once after: a few 1e-3 at most
+        assert frob_row < 4e-3, (rank, frob_row)
+        assert frob_moe < 4e-3, (rank, frob_moe)
