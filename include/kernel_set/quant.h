@@ -3,8 +3,8 @@
  *
  * Replaces three entries of include/kernel_set/quant.h of the reference
  * project: ks_quantize_fp8_group (:28-40), ks_dequantize_int4 (:53-58) and
- * ks_repack_int4 (:60-66). The per-tensor fp8, int8 and nvfp4 quantizers of
- * that header are other formats and are not exported here.
+ * ks_repack_int4 (:60-66), and adds the import of GPTQ / AWQ checkpoints. The
+ * per-tensor fp8, int8 and nvfp4 quantizers of that header are other formats.
  */
 #ifndef KERNEL_SET_QUANT_H_
 #define KERNEL_SET_QUANT_H_
@@ -51,9 +51,12 @@ KS_API ks_status_t ks_dequantize_int4(void* out, const void* qweight_packed,
 
 /*
  * Re-lays the int32 [K/8, N] packing above into the uint8 [K/2, N] packing
- * that ks_gemm_w4a16 reads (even k in the low nibble). `num_bits` must be 4;
- * a non-NULL `perm` (activation reordering) returns KS_ERROR_NOT_IMPLEMENTED.
- * Contract as the reference: quant.h:60-66, repack_int4.cu:43-70.
+ * that ks_gemm_w4a16 reads (even k in the low nibble). `num_bits` must be 4.
+ * `perm`: NULL, or int32 [size_k] on the device, a permutation of 0..size_k-1:
+ * row k' of the result is then row perm[k'] of the source (activation order;
+ * the reference returns KS_ERROR_NOT_IMPLEMENTED for it). An entry outside
+ * 0..size_k-1 yields code 0. With perm, size_k and size_n must be multiples
+ * of 8. Contract otherwise as the reference: quant.h:60-66, repack_int4.cu:43-70.
  */
 KS_API ks_status_t ks_repack_int4(void* out_packed, const void* qweight,
                                   const void* perm, int64_t size_k,
@@ -77,6 +80,63 @@ KS_API ks_status_t ks_quantize_fp8_group_colscale(void* out, float* scale_t,
                                                   ks_dtype_t in_dtype,
                                                   ks_dtype_t fp8_dtype,
                                                   ks_stream_t stream);
+
+/*
+ * Import of int4 checkpoints. No counterpart in the reference's C ABI: its
+ * documentation names the missing re-layout as a gap (docs/QUANT_OPERATORS.md:
+ * 71-75, 165) and its dispatcher hands the op to external providers
+ * (bindings/python/kernel_set/backends/_quant_ext.py:217-241).
+ *
+ *   GPTQ  qweight [K/8, N] int32, code of k = 8*row + j in bits 4j..4j+3
+ *         qzeros  [G, N/8] int32, column 8c+j in bits 4j..4j+3; files of the
+ *                 first format version store zero-1 (zero_offset = 1)
+ *         g_idx   [K] group of each row when quantised in activation order;
+ *                 perm = stable argsort(g_idx) makes the groups contiguous
+ *   AWQ   qweight [K, N/8] int32, qzeros [G, N/8] int32; column 8c+j in nibble
+ *         {0,4,1,5,2,6,3,7}[j] of word c; zero_offset = 0
+ */
+typedef enum ks_int4_source_t {
+  KS_INT4_SOURCE_GPTQ = 0,
+  KS_INT4_SOURCE_AWQ = 1
+} ks_int4_source_t;
+
+typedef enum ks_int4_packing_t {
+  KS_INT4_PACKING_BYTES = 0, /* uint8 [K/2, N], what ks_gemm_w4a16 reads     */
+  KS_INT4_PACKING_WORDS = 1  /* int32 [K/8, N], what ks_dequantize_int4 reads */
+} ks_int4_packing_t;
+
+/*
+ * Writes the codes of a checkpoint's qweight in one of the two packings of
+ * this library. `perm` as in ks_repack_int4 (NULL: rows keep their order).
+ * size_k and size_n multiples of 8; both pointers 16-byte aligned.
+ */
+KS_API ks_status_t ks_int4_import_weight(void* out, const void* qweight,
+                                         const int32_t* perm, int64_t size_k,
+                                         int64_t size_n,
+                                         ks_int4_source_t source,
+                                         ks_int4_packing_t packing,
+                                         ks_stream_t stream);
+
+/*
+ * zeros[g, n] = code(qzeros, g, n) + zero_offset, as `out_dtype` (f32 / f16 /
+ * bf16): the [G, N] zero-points that ks_gemm_w4a16 and ks_dequantize_int4
+ * read. zero_offset 0 or 1; size_n a multiple of 8.
+ */
+KS_API ks_status_t ks_int4_import_zeros(void* zeros, const void* qzeros,
+                                        int64_t groups, int64_t size_n,
+                                        ks_int4_source_t source,
+                                        int zero_offset, ks_dtype_t out_dtype,
+                                        ks_stream_t stream);
+
+/*
+ * out[r, j] = input[r, perm[j]]: the activations of a layer whose weight rows
+ * were reordered with the same perm. perm int32 [cols]; an entry outside
+ * 0..cols-1 yields 0. out must not alias input.
+ */
+KS_API ks_status_t ks_gather_columns(void* out, const void* input,
+                                     const int32_t* perm, int64_t rows,
+                                     int64_t cols, ks_dtype_t dtype,
+                                     ks_stream_t stream);
 
 KS_END_EXTERN_C
 

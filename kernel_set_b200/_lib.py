@@ -174,6 +174,9 @@ _decl("ks_quantize_fp8_group", [_VP, POINTER(c_float), _VP, c_int64, c_int64, c_
 _decl("ks_quantize_fp8_group_colscale", [_VP, POINTER(c_float), c_int64, _VP, c_int64, c_int64, c_int, c_int, _VP])
 _decl("ks_dequantize_int4", [_VP, _VP, _VP, _VP, c_int64, c_int64, c_int, c_int, _VP])
 _decl("ks_repack_int4", [_VP, _VP, _VP, c_int64, c_int64, c_int, _VP])
+_decl("ks_int4_import_weight", [_VP, _VP, _VP, c_int64, c_int64, c_int, c_int, _VP])
+_decl("ks_int4_import_zeros", [_VP, _VP, c_int64, c_int64, c_int, c_int, c_int, _VP])
+_decl("ks_gather_columns", [_VP, _VP, _VP, c_int64, c_int64, c_int, _VP])
 
 # moe.h
 _decl("ks_moe_gate_softmax_topk", [POINTER(c_float), POINTER(c_int32), _VP, c_int64, c_int, c_int, c_int, c_int, _VP])

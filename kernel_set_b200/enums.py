@@ -40,3 +40,13 @@ class QuantMode(IntEnum):
     PER_TOKEN = 1
     PER_CHANNEL = 2
     GROUPWISE = 3
+
+
+class Int4Source(IntEnum):
+    GPTQ = 0
+    AWQ = 1
+
+
+class Int4Packing(IntEnum):
+    BYTES = 0   # uint8 [K/2, N]: what gemm_w4a16 reads
+    WORDS = 1   # int32 [K/8, N]: what dequantize_int4 reads

@@ -162,9 +162,81 @@ def pack_int4_bytes(codes: torch.Tensor) -> torch.Tensor:
     return (c[0::2] | (c[1::2] << 4)).to(torch.uint8)
 
 
-def repack_int4(qweight: torch.Tensor) -> torch.Tensor:
-    """int32 [K/8, N] -> uint8 [K/2, N] (kernels/src/quant/repack_int4.cu:10-34)."""
-    return pack_int4_bytes(unpack_int4_words(qweight))
+def repack_int4(qweight: torch.Tensor, perm: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """int32 [K/8, N] -> uint8 [K/2, N] (kernels/src/quant/repack_int4.cu:10-34).
+    ``perm``: row k' of the result is row perm[k'] of the source, the meaning the
+    argument has in the provider the reference routes the op to
+    (bindings/python/kernel_set/backends/_quant_ext.py:217-227); the reference's
+    own kernel refuses it (repack_int4.cu:52-53)."""
+    codes = unpack_int4_words(qweight)
+    if perm is not None:
+        codes = codes[perm.long()]
+    return pack_int4_bytes(codes)
+
+
+# Checkpoint formats. The reference holds no code for them (its documentation
+# names the gap, docs/QUANT_OPERATORS.md:71-75, 165); these are the published
+# layouts of the GPTQ and AWQ file formats, pinned in tests/golden against the
+# packers of the provider the reference routes the op to.
+AWQ_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)     # nibble i of a word holds column 8c + AWQ_ORDER[i]
+
+
+def _to_i32(word: torch.Tensor) -> torch.Tensor:
+    return torch.where(word >= 2 ** 31, word - 2 ** 32, word).to(torch.int32)
+
+
+def pack_cols(values: torch.Tensor, order: Sequence[int] = tuple(range(8))) -> torch.Tensor:
+    """[R, N] codes -> int32 [R, N/8]; nibble i of word c holds column 8c + order[i]."""
+    r, n = values.shape
+    v = values.to(torch.int64).view(r, n // 8, 8)
+    word = torch.zeros(r, n // 8, dtype=torch.int64)
+    for i, col in enumerate(order):
+        word |= (v[:, :, col] & 0xF) << (4 * i)
+    return _to_i32(word)
+
+
+def unpack_cols(words: torch.Tensor, order: Sequence[int] = tuple(range(8))) -> torch.Tensor:
+    """Inverse of :func:`pack_cols`: int32 [R, N/8] -> codes int32 [R, N]."""
+    r, nc = words.shape
+    w = words.to(torch.int64) & 0xFFFFFFFF
+    out = torch.zeros(r, nc, 8, dtype=torch.int32)
+    for i, col in enumerate(order):
+        out[:, :, col] = ((w >> (4 * i)) & 0xF).to(torch.int32)
+    return out.view(r, nc * 8)
+
+
+def gptq_checkpoint(codes: torch.Tensor, zeros: torch.Tensor, zero_offset: int = 1):
+    """codes [K, N], zero-points [G, N] -> (qweight [K/8, N], qzeros [G, N/8]) as a GPTQ
+    file holds them: codes packed along K, zero-points minus ``zero_offset`` along N."""
+    return pack_int4_words(codes), pack_cols(zeros - zero_offset)
+
+
+def awq_checkpoint(codes: torch.Tensor, zeros: torch.Tensor):
+    """codes [K, N], zero-points [G, N] -> (qweight [K, N/8], qzeros [G, N/8]) as an AWQ
+    (GEMM format) file holds them: both packed along N in the interleaved order."""
+    return pack_cols(codes, AWQ_ORDER), pack_cols(zeros, AWQ_ORDER)
+
+
+def import_int4_weight(qweight: torch.Tensor, source: str, packing: str = "bytes",
+                       perm: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Checkpoint qweight -> uint8 [K/2, N] (``packing="bytes"``) or int32 [K/8, N]
+    (``"words"``); ``perm`` as in :func:`repack_int4`."""
+    codes = unpack_int4_words(qweight) if source == "gptq" else unpack_cols(qweight, AWQ_ORDER)
+    if perm is not None:
+        codes = codes[perm.long()]
+    return pack_int4_bytes(codes) if packing == "bytes" else pack_int4_words(codes)
+
+
+def import_int4_zeros(qzeros: torch.Tensor, source: str, zero_offset: int, dtype=torch.float32) -> torch.Tensor:
+    """Packed zero-points [G, N/8] -> [G, N] = code + zero_offset in ``dtype``."""
+    codes = unpack_cols(qzeros) if source == "gptq" else unpack_cols(qzeros, AWQ_ORDER)
+    return (codes + zero_offset).to(dtype)
+
+
+def act_order_perm(g_idx: torch.Tensor) -> torch.Tensor:
+    """The row order that makes the groups of an activation-ordered GPTQ layer
+    contiguous: a stable argsort of g_idx."""
+    return torch.argsort(g_idx.long(), stable=True).to(torch.int32)
 
 
 def dequantize_int4(qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group_size: int,

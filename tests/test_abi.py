@@ -33,7 +33,7 @@ def test_headers_compile_as_c_and_cpp(tmp_path):
 
 def test_every_declared_symbol_is_exported(ks):
     decl = declared_symbols()
-    assert len(decl) == 41, decl
+    assert len(decl) == 44, decl
     out = subprocess.run(["nm", "-D", "--defined-only", ks.LIB_PATH], capture_output=True, text=True, check=True)
     exported = sorted(l.split()[-1] for l in out.stdout.splitlines() if " T " in l)
     assert [s for s in decl if s not in exported] == []
@@ -133,7 +133,19 @@ def test_argument_validation_codes(ks):
     rp = L.ks_repack_int4
     assert rp(ONE, None, None, 8, 8, 4, None) == S.INVALID_ARGUMENT
     assert rp(ONE, ONE, None, 8, 8, 8, None) == S.INVALID_ARGUMENT
-    assert rp(ONE, ONE, ONE, 8, 8, 4, None) == S.NOT_IMPLEMENTED
+    assert rp(ONE, ONE, ONE, 12, 8, 4, None) == S.UNSUPPORTED_SHAPE      # activation order: K, N multiples of 8
+    iw, iz, gc = L.ks_int4_import_weight, L.ks_int4_import_zeros, L.ks_gather_columns
+    assert iw(ONE, None, None, 8, 8, 0, 0, None) == S.INVALID_ARGUMENT
+    assert iw(ONE, ONE, None, 8, 8, 2, 0, None) == S.INVALID_ARGUMENT
+    assert iw(ONE, ONE, None, 8, 8, 0, 2, None) == S.INVALID_ARGUMENT
+    assert iw(ONE, ONE, None, 12, 8, 0, 0, None) == S.UNSUPPORTED_SHAPE
+    assert iz(ONE, ONE, 1, 8, 0, 2, D.F16, None) == S.INVALID_ARGUMENT
+    assert iz(ONE, ONE, 1, 12, 0, 1, D.F16, None) == S.UNSUPPORTED_SHAPE
+    assert iz(ONE, ONE, 1, 8, 0, 1, D.I32, None) == S.UNSUPPORTED_DTYPE
+    assert gc(P(32), ONE, None, 1, 8, D.F16, None) == S.INVALID_ARGUMENT
+    assert gc(ONE, ONE, ONE, 1, 8, D.F16, None) == S.INVALID_ARGUMENT        # out aliases input
+    assert gc(P(32), ONE, ONE, 1, 8, D.I8, None) == S.UNSUPPORTED_DTYPE
+    assert gc(P(32), ONE, ONE, 70000, 8, D.F16, None) == S.UNSUPPORTED_SHAPE
     # ks_moe_grouped_gemm (reference moe_grouped_gemm.cu:140-153)
     gg = L.ks_moe_grouped_gemm
     assert gg(ONE, ONE, ONE, i32p(None), 2, 8, 8, 8, D.BF16, None) == S.INVALID_ARGUMENT

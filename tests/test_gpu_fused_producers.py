@@ -1,7 +1,9 @@
 """GPU: the quantizer fused into its producers and the column-major scale layout.
 
 RMSNorm follows the reference's torch statement (benchmarks/bench.py:877-879) up to the
-reciprocal square root (one unit in the last place of the output at most); the fused forms
+reciprocal square root and the order of the sum of squares: a last-place difference there can
+flip the rounding of the intermediate `T(x * inv_rms)`, which the second rounding after the
+weight can widen to two units in the last place of the output, rarely; the fused forms
 must equal the unfused library calls run one after the other bit for bit; the GEMM fed with
 column-major scales must equal the GEMM fed with row-major ones bit for bit."""
 import pytest
@@ -29,7 +31,7 @@ def test_rms_norm(ks, cuda, rows, cols, dtype):
     torch.cuda.synchronize()
     ref = orc.rms_norm(x, w, 1e-6).float()
     got = out.cpu().float()
-    tol = {torch.float32: 3e-6, torch.float16: 1.2e-3, torch.bfloat16: 9e-3}[dtype]
+    tol = {torch.float32: 3e-6, torch.float16: 2.1e-3, torch.bfloat16: 1.6e-2}[dtype]   # two units in the last place
     assert float(((got - ref).abs() / (ref.abs() + 1e-3)).max()) < tol
     assert orc.rel_err_max(got, ref) < tol
     if dtype != torch.float32:

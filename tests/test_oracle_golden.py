@@ -114,3 +114,31 @@ def test_e4m3_cast_saturation_domain():
     # non-saturating torch cast and a saturating hardware cast agree.
     v = torch.tensor([447.9, 448.0, 448.00003, 463.9])
     assert torch.equal(v.to(torch.float8_e4m3fn).float(), torch.full((4,), 448.0))
+
+
+def test_int4_checkpoint_formats_match_provider_packers():
+    """The oracle's statement of the GPTQ and AWQ file layouts against vectors packed by the
+    provider's own packers (tests/golden/make_int4_checkpoint_golden.py)."""
+    g = golden("int4_checkpoint.npz")
+    t = {k: torch.from_numpy(v) for k, v in g.items() if getattr(v, "ndim", 0) > 0}
+    codes, gs = t["codes"], int(g["group_size"])
+    qw, qz1 = orc.gptq_checkpoint(codes, t["zeros_gptq"], zero_offset=1)
+    assert torch.equal(qw, t["gptq_qweight"]) and torch.equal(qz1, t["gptq_qzeros_v1"])
+    assert torch.equal(orc.gptq_checkpoint(codes, t["zeros_awq"], zero_offset=0)[1], t["gptq_qzeros_v2"])
+    aw, az = orc.awq_checkpoint(codes, t["zeros_awq"])
+    assert torch.equal(aw, t["awq_qweight"]) and torch.equal(az, t["awq_qzeros"])
+    # import: both formats give the same codes and zero-points back, in both packings
+    want_bytes, want_words = orc.pack_int4_bytes(codes), orc.pack_int4_words(codes)
+    for src, q in (("gptq", t["gptq_qweight"]), ("awq", t["awq_qweight"])):
+        assert torch.equal(orc.import_int4_weight(q, src, "bytes"), want_bytes)
+        assert torch.equal(orc.import_int4_weight(q, src, "words"), want_words)
+    assert torch.equal(orc.import_int4_zeros(t["gptq_qzeros_v1"], "gptq", 1, torch.int32), t["zeros_gptq"])
+    assert torch.equal(orc.import_int4_zeros(t["gptq_qzeros_v2"], "gptq", 0, torch.int32), t["zeros_awq"])
+    assert torch.equal(orc.import_int4_zeros(t["awq_qzeros"], "awq", 0, torch.int32), t["zeros_awq"])
+    # activation order: sorting the stored rows by group gives a layer whose group of row k' is k' // gs,
+    # and whose rows are those of the unpermuted layer in the order rows[perm]
+    perm = orc.act_order_perm(t["g_idx"])
+    assert torch.equal(t["g_idx"][perm.long()].long(), torch.arange(codes.shape[0]) // gs)
+    got = orc.unpack_int4_bytes(orc.repack_int4(t["gptq_qweight_act_order"], perm))
+    assert torch.equal(got, codes[t["act_order_rows"][perm.long()]])
+    assert torch.equal(orc.repack_int4(t["gptq_qweight"]), want_bytes)
