@@ -260,6 +260,12 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
   const int lane = threadIdx.x & 31;
   const WaitCtx wctx{abort_flag, p.fault_word};
 
+  // Programmatic dependent launch: the next kernel on the stream may start its prologue now;
+  // this one reads what the kernel before it may have produced (quantised activations and
+  // their scales, expert offsets) and writes its outputs only behind grid_dependency_wait():
+  // in the producer warp, in the epilogue warps and, for grouped problems, before the
+  // offsets are read.
+  grid_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
@@ -280,6 +286,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     tmem_relinquish();
   }
   if constexpr (GROUPED) {
+    grid_dependency_wait();
     // offs[e] = first row of expert e; with the masked layout the rows of an expert end at
     // offs[e] + masked_m[e] instead of at offs[e + 1] (ends[] holds either)
     int* ends = offs + (kMaxExperts + 1);
@@ -315,6 +322,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if constexpr (C::kRebalanceRegs) setmaxnreg_dec<C::kRegsIssue>();
+    grid_dependency_wait();
     uint32_t it = 0;
     bool ok = true;
     TileCoord tc;
@@ -390,6 +398,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
   } else if (warp >= 4) {
     // -------------------------------- epilogue --------------------------------
     if constexpr (C::kRebalanceRegs) setmaxnreg_inc<C::kRegsEpi>();
+    grid_dependency_wait();
     const int quarter = warp & 3;         // TMEM lane quarter this warp can address
     const int slice = (warp - 4) >> 2;    // which kEpiCols-wide column slice of the tile
     constexpr int EC = C::kEpiCols;
@@ -605,6 +614,8 @@ split_reduce_kernel(OutT* __restrict__ out, const float4* __restrict__ slots, in
   constexpr int EC = C::kEpiCols;
   constexpr int kChunks = EC / 4;
   constexpr int kPerTile = C::kEpiWarps * kChunks * 32;   // float4 per (tile, part)
+  grid_launch_dependents();
+  grid_dependency_wait();   // the parts are the GEMM kernel's output
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= tails * kPerTile) return;
   const int tail = idx / kPerTile;
@@ -687,14 +698,17 @@ ks_status_t launch_one(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUte
                                                                        : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     if (tma_encode(&tm_c, dt, 2, a.out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) p.tma_store = 1;
   }
-  kernel<<<grid, C::kThreads, C::smem_bytes(GROUPED), stream>>>(tm_a, tm_b, tm_c, p);
+  cudaError_t le = launch_programmatic(kernel, static_cast<unsigned>(grid), C::kThreads, C::smem_bytes(GROUPED), stream,
+                                       tm_a, tm_b, tm_c, p);
+  if (le != cudaSuccess) return cuda_status(le, a.where);
   if constexpr (!GROUPED) {
     if (p.split_s > 1) {
       const int tails = p.split_items / p.split_s;
       const int work = tails * C::kEpiWarps * (C::kEpiCols / 4) * 32;
-      split_reduce_kernel<BN, OutT><<<(work + 255) / 256, 256, 0, stream>>>(
-          static_cast<OutT*>(p.out), p.split_slots, p.split_from, p.split_s, tails, p.tiles_m, p.tiles_n, p.m, p.n,
-          p.vec_store);
+      le = launch_programmatic(split_reduce_kernel<BN, OutT>, static_cast<unsigned>((work + 255) / 256), 256u, 0, stream,
+                               static_cast<OutT*>(p.out), static_cast<const float4*>(p.split_slots), p.split_from,
+                               p.split_s, tails, p.tiles_m, p.tiles_n, p.m, p.n, p.vec_store);
+      if (le != cudaSuccess) return cuda_status(le, a.where);
     }
   }
   return cuda_status(cudaGetLastError(), a.where);

@@ -1,5 +1,7 @@
 #include "sm100_host.cuh"
 
+#include <cstdlib>
+
 #include <map>
 #include <mutex>
 #include <utility>
@@ -120,6 +122,11 @@ void stream_scratch_release(cudaStream_t stream) {
     }
   }
   cudaGetLastError();
+}
+
+bool programmatic_launch_enabled() {
+  static const bool enabled = std::getenv("KS_B200_NO_PDL") == nullptr;
+  return enabled;
 }
 
 }  // namespace sm100

@@ -38,5 +38,30 @@ bool stream_scratch_take_dirty(cudaStream_t stream, int kind);
 // called when the stream is destroyed, so that a recycled handle starts clean.
 void stream_scratch_release(cudaStream_t stream);
 
+// Launches `kernel` with programmatic stream serialization: it may begin while the kernel
+// before it on the stream is still running, once every CTA of that kernel has executed
+// griddepcontrol.launch_dependents or exited (a kernel that never executes it is simply
+// waited for, as in an ordinary launch). The launched kernel must order its own accesses
+// with griddepcontrol.wait (grid_dependency_wait() in sm100_ptx.cuh).
+// False when the environment variable KS_B200_NO_PDL is set (read once): launch_programmatic
+// then launches the ordinary way.
+bool programmatic_launch_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_programmatic(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem,
+                                       cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = programmatic_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace sm100
 }  // namespace ksb

@@ -185,6 +185,16 @@ __device__ __forceinline__ bool mbar_wait(const WaitCtx& ctx, uint32_t bar, uint
   }
 }
 
+// ---- programmatic dependent launch --------------------------------------------------
+// A kernel launched with programmatic stream serialization may start while the kernel before
+// it on the stream is still running. grid_dependency_wait() returns once that kernel has
+// completed and its writes are visible: every thread that reads what it produced, or
+// overwrites what it may still read, calls it first. grid_launch_dependents() tells the
+// runtime that the NEXT kernel on the stream may begin to occupy free resources. Both are
+// no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
 // ---- TMA (tiled bulk tensor loads, one CTA, completion on an mbarrier) --------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -269,6 +269,10 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   }
   const uint32_t act_tx = static_cast<uint32_t>(p.mt) * kStepK * 2;
   const uint32_t raw_tx = kRawBytes + 256 + (p.has_zeros ? 256 : 0);
+  // The next kernel on the stream may start its prologue now. This one touches what the
+  // kernel before it may have produced or may still read (activations, C, the split-K
+  // scratch) only behind grid_dependency_wait(): the activation producer and the epilogue.
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------- weight producer (TMA) -------------------------
@@ -308,6 +312,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
   } else if (warp == 2) {
     // ----------------------- activation producer (TMA) -----------------------
+    grid_dependency_wait();
     uint32_t it = 0;
     int mtile = static_cast<int>(u_begin / units);
     int step = static_cast<int>((u_begin - static_cast<long long>(mtile) * units) % p.k_steps);
@@ -616,6 +621,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const int quarter = warp & 3;
     const int n_local = quarter * 32 + lane;   // TMEM lane = weight column inside the tile
     const int et = threadIdx.x - (128 + C::kDeqWarps * 32);
+    grid_dependency_wait();
     T* c = static_cast<T*>(p.c);
     const T* bias = static_cast<const T*>(p.bias);
     uint32_t seg = 0;
@@ -753,8 +759,9 @@ ks_status_t launch_t(const W4A16Args& a, const CUtensorMap& tm_w, const CUtensor
       attr_done[dev] = true;
     }
   }
-  kernel<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tm_w, tm_s, tm_z, tm_a, p);
-  return cuda_status(cudaGetLastError(), "ks_gemm_w4a16");
+  return cuda_status(launch_programmatic(kernel, static_cast<unsigned>(grid), C::kThreads, C::kSmemBytes, stream, tm_w,
+                                         tm_s, tm_z, tm_a, p),
+                     "ks_gemm_w4a16");
 }
 
 }  // namespace
@@ -874,23 +881,23 @@ ks_status_t enqueue_w4a16(const W4A16Args& a, const Geometry& g, unsigned int* c
 
 // Which fast kernel. The register-operand decode kernel feeds legacy mma.sync, whose rate on
 // this part is about a tenth of tcgen05's (measured: ~100 bf16 FMA per clock and SM
-// sub-partition): with 8 tokens (one MMA per 16 x 16 weight block) it is ahead of the tcgen05
-// kernel on wide weights (K=4096, N=28672: 28.9 us against 33.7), at 16 tokens they are level,
-// beyond that it is MMA-bound (32 tokens: 46 us against 37). On problems with few units per
-// CTA (K=14336, N=4096: 6 per CTA) its pipeline fill and the split-K fix-up of every CTA cost
-// more than they save (24.7 us against 22.8). Chosen: at most 8 tokens and at least 10 units
-// per CTA; the caller can pin either kernel.
+// sub-partition): up to 8 tokens (one MMA per 16 x 16 weight block) it is well ahead of the
+// tcgen05 kernel on wide weights (K=4096, N=28672, queued launches: 24.6 us against 29.7), at
+// 16 tokens slightly (29.0 against 30.4), beyond that it is MMA-bound (32 tokens: 41 us
+// against 33). On problems with few units per CTA (K=14336, N=4096: 6 per CTA) its pipeline
+// fill and the split-K fix-up of every CTA cost what they save (19.8 us against 19.1).
+// Chosen: at most 16 tokens and at least 10 units per CTA; the caller can pin either kernel.
 bool use_decode_kernel(const W4A16Args& a) {
   if (a.kernel == 1 || !decode::eligible(a)) return false;
   if (a.kernel == 2 || !w4a16_eligible(a)) return true;
   const long long units = ((a.n + 255) / 256) * (a.k / 128);
-  return a.m <= 8 && units >= 20ll * sm_count();
+  return a.m <= 16 && units >= 20ll * sm_count();
 }
 
 ks_status_t launch_w4a16(const W4A16Args& a, cudaStream_t stream) {
   // Counters and slots are separate allocations: the counters must be zero whenever no
   // kernel is running, and a region that another shape used for partial sums is not.
-  // The tcgen05 kernel can give up on a bounded wait and leave counters non-zero; when
+  // The tcgen05 kernels can give up on a bounded wait and leave counters non-zero; when
   // the fault poll has reported such a launch on this device, every stream's counters are
   // cleared before their next use (stream_scratch_dirty).
   const bool dec = use_decode_kernel(a);
@@ -984,8 +991,8 @@ ks_status_t launch_w4a16_static(const W4A16Args& a, cudaStream_t stream) {
   if (dec) return decode::enqueue(a, gd, counters, slots, stream);
   // The word through which a tcgen05 kernel reports a bounded wait that ran out is a pinned
   // host allocation made by the first allocating entry point on the device; a process that
-  // only ever calls this entry point runs the tcgen05 kernel without it (the decode kernel,
-  // which serves up to 64 rows, has no such wait).
+  // only ever calls this entry point runs the tcgen05 kernel without it (the decode kernel
+  // has no such wait).
   return enqueue_w4a16(a, g, counters, slots, kernel_fault_word_if_ready(), stream);
 }
 

@@ -23,8 +23,8 @@ struct W4A16Args {
   // token rows) to the tensor core: 0 = choose (tensor memory), 1 = shared memory,
   // 2 = tensor memory.
   int operand_path = 0;
-  // Which fast kernel: 0 = choose (the register-operand decode kernel up to
-  // decode::kMaxTokens rows, the tcgen05 kernel above), 1 = tcgen05, 2 = decode.
+  // Which fast kernel: 0 = choose, 1 = tcgen05 (sm100_w4a16.cu), 2 = register-operand
+  // decode kernel (w4a16_decode.cu).
   int kernel = 0;
 };
 

@@ -47,7 +47,11 @@
 #include <mutex>
 #include <type_traits>
 
+#include <cstdlib>
+
 #include "common.cuh"
+#include "sm100_host.cuh"
+#include "sm100_ptx.cuh"
 #include "sm100_w4a16.cuh"
 
 namespace ksb {
@@ -206,6 +210,8 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, s = lane & 3;
+  // the next kernel on the stream may start its own prologue as soon as it finds room
+  grid_launch_dependents();
 
   const long long units = static_cast<long long>(p.n_tiles) * p.k_steps;
   const int ctas = gridDim.x;
@@ -252,17 +258,26 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
     sz_src = s_ok ? sz_base + (static_cast<size_t>(grp) * p.n + col0 + lane * 8) * 2 : a_bytes;
   };
   enter_tile(tile_l, step_l, grp_l);
-  auto issue = [&]() {
+  // The activations may be the output of the kernel that runs before this one on the stream;
+  // the weights are not. A launch with programmatic stream serialization starts while that
+  // kernel is still running, so the prologue copies weights, scales and zero-points only and
+  // hands in the activations of the same units after the grid dependency has resolved.
+  auto issue_x = [&](uint32_t stage, const uint8_t* src) {
+#pragma unroll
+    for (int i = 0; i < kXChunks; ++i) {
+      if (16 * i + 15 < C::kTokens || static_cast<int>(ld_r0) + 16 * i < C::kTokens)
+        cp_async16(stage + x_dst + i * (16 * kStepK * 2), x_bytes[i] ? src + i * x_row16 : a_bytes, x_bytes[i]);
+    }
+  };
+  const uint8_t* late_x_src[S - 1];
+  auto issue = [&](auto with_x_tag, int slot) {
+    constexpr bool kWithX = decltype(with_x_tag)::value;
     if (loaded < n_units) {
       // a chunk outside the matrix keeps the (valid) base pointer and copies zero bytes
       const size_t wr = w_bytes ? w_row16 : 0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) cp_async16(st_load + w_dst + i * (16 * kTileN), w_src + i * wr, w_bytes);
-#pragma unroll
-      for (int i = 0; i < kXChunks; ++i) {
-        if (16 * i + 15 < C::kTokens || static_cast<int>(ld_r0) + 16 * i < C::kTokens)
-          cp_async16(st_load + x_dst + i * (16 * kStepK * 2), x_bytes[i] ? x_src + i * x_row16 : a_bytes, x_bytes[i]);
-      }
+      if constexpr (kWithX) issue_x(st_load, x_src); else late_x_src[slot] = x_src;
       if (sz_active) cp_async16(st_load + sz_dst, sz_src, sz_bytes);
       ++loaded;
       st_load = (st_load == ring + (S - 1) * C::kStageBytes) ? ring : st_load + C::kStageBytes;
@@ -355,8 +370,15 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
   };
 
   // prologue: S-1 units on their way; the first one's activations in consumer order
-#pragma unroll 1
-  for (int i = 0; i < S - 1; ++i) issue();
+#pragma unroll
+  for (int i = 0; i < S - 1; ++i) issue(std::false_type{}, i);
+  grid_dependency_wait();   // everything the previous kernel wrote is visible from here on
+#pragma unroll
+  for (int i = 0; i < S - 1; ++i) {
+    if (i < n_units) issue_x(ring + i * C::kStageBytes, late_x_src[i]);
+    cp_async_commit();
+  }
+  // groups so far: S-1 of weights, then S-1 of activations; the first S of them cover unit 0
   cp_async_wait<S - 2>();
   permute_x(ring);
   uint32_t st = ring;            // stage of the unit being computed
@@ -367,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
     cp_async_wait<S - 3>();   // this thread's copies of units it and it+1 have landed ...
     __syncthreads();          // ... everyone's of unit it (and its permuted activations) too;
                               // and everyone has finished reading unit it-1
-    issue();                  // refill the stage unit it-1 occupied
+    issue(std::true_type{}, 0);   // refill the stage unit it-1 occupied
     if (it + 1 < n_units) permute_x(st_next);   // own chunks only: no other thread touches them before the next barrier
 
     // scales and zero-points of this lane's columns: chunk c, columns 2g and 2g+1
@@ -532,8 +554,8 @@ ks_status_t launch_t(const Params& p, int grid, cudaStream_t stream) {
       attr_done[dev] = true;
     }
   }
-  kernel<<<grid, kThreads, C::kSmemBytes, stream>>>(p);
-  return cuda_status(cudaGetLastError(), "ks_gemm_w4a16");
+  return cuda_status(launch_programmatic(kernel, static_cast<unsigned>(grid), kThreads, C::kSmemBytes, stream, p),
+                     "ks_gemm_w4a16");
 }
 
 template <typename T>
