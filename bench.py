@@ -522,6 +522,41 @@ def run_cfg5(args, torch, dist, ks, parallel, dev, rank, world):
         fp32 = {"ms_per_step": float(t32[0]), "allreduce_us": float(t32[1]) * 1e3,
                 "value": 2.0 * m5 * n5 * k5 / (float(t32[0]) * 1e-3) / 1e12, "parity": par32}
         del out32
+    # the all-reduce fused with the GEMM over peer memory: every rank's epilogue stores its
+    # partial of a row block into the owner's memory, the owner adds the slots in fp32 and
+    # writes the rows into every rank's output (kernel_set_b200.parallel.FusedRowParallel)
+    fused = None
+    if world > 1:
+        try:
+            fused = {}
+            for tag, pdt in (("fp32_slots", torch.float32), ("bf16_slots", torch.bfloat16)):
+                layer = parallel.FusedRowParallel(m5, n5, part_dtype=pdt, device=dev)
+
+                def step_fused():
+                    quant()
+                    layer.multiply(a8, a_s, w8, ws)
+
+                def reduce_scatter_only():
+                    quant()
+                    layer.multiply(a8, a_s, w8, ws, gather=False)
+
+                res = layer.multiply(a8, a_s, w8, ws)
+                barrier()
+                parf = None
+                if rank == 0:
+                    gotf = res[:win, :win].float().cpu()
+                    ef = ((gotf - ref32).abs() / orc.bf16_ulp(ref32).float())
+                    parf = {"rel_frobenius": orc.rel_frobenius(gotf, ref32.to(torch.bfloat16).float()),
+                            "max_err_bf16_ulp": float(ef.max()), "frac_above_2_ulp": float((ef > 2).float().mean())}
+                tf = torch.tensor([timed(step_fused, steps, 1, barrier, torch), timed(reduce_scatter_only, steps, 1, barrier, torch)],
+                                  dtype=torch.float64, device=dev)
+                dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+                fused[tag] = {"ms_per_step": float(tf[0]), "value": 2.0 * m5 * n5 * k5 / (float(tf[0]) * 1e-3) / 1e12,
+                              "ms_per_step_reduce_scatter_only": float(tf[1]), "parity": parf}
+                del layer, res
+                torch.cuda.empty_cache()
+        except Exception as exc:   # symmetric memory not available on this machine
+            fused = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
     t = torch.tensor([ms_step, ms_quant, ms_gemm, ms_red], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -538,7 +573,7 @@ def run_cfg5(args, torch, dist, ks, parallel, dev, rank, world):
         "gemm_us": ms_gemm * 1e3, "quantizer_us": ms_quant * 1e3, "allreduce_us": ms_red * 1e3,
         "gemm_tflops_per_gpu": flops / world / (ms_gemm * 1e-3) / 1e12,
         "allreduce_busbw_gbs": (ring_bytes / (ms_red * 1e-3) / 1e9) if world > 1 else None,
-        "parity": parity, "fp32_partials": fp32}
+        "parity": parity, "fp32_partials": fp32, "fused_over_peer_memory": fused}
 
 
 def moe_small_parity(torch, dist, ks, parallel, dev, rank, world):

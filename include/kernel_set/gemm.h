@@ -177,6 +177,46 @@ KS_API ks_status_t ks_gemm_fp8_blockwise_colscale(void* out, const void* a_fp8,
                                                   ks_dtype_t out_dtype,
                                                   ks_stream_t stream);
 
+/*
+ * The block-scaled GEMM with a scattered output, for a row-parallel (K-split)
+ * layer: rows [b * rows_per_part, (b + 1) * rows_per_part) of this call's product
+ * are written to out_parts[b], a [rows_per_part, n] matrix of `out_dtype` that may
+ * live in another GPU's memory (a peer-mapped address, e.g. rank b's buffer of a
+ * symmetric allocation, offset to the slot of the calling rank). The finished
+ * tiles leave by TMA stores, so the transfer over NVLink runs under the tiles
+ * still being computed; ks_sum_parts on the owning rank then adds the ranks'
+ * slots. `out_parts` is a HOST array of num_parts (1..8) device pointers.
+ * rows_per_part a multiple of 128, m = num_parts * rows_per_part, rows 16-byte
+ * aligned. Only the tcgen05 kernel serves this entry. No counterpart in the
+ * reference, which has no multi-GPU path.
+ */
+KS_API ks_status_t ks_gemm_fp8_blockwise_scatter(void* const* out_parts,
+                                                 int num_parts,
+                                                 int64_t rows_per_part,
+                                                 const void* a_fp8,
+                                                 const void* b_fp8,
+                                                 const float* a_scale,
+                                                 const float* b_scale,
+                                                 int64_t m, int64_t n,
+                                                 int64_t k, int b_layout,
+                                                 ks_dtype_t fp8_dtype,
+                                                 ks_dtype_t out_dtype,
+                                                 ks_stream_t stream);
+
+/*
+ * out = sum over q of parts[q], parts [num_parts, rows, n] of `part_dtype`
+ * (f32 / f16 / bf16), added in part order in fp32 and rounded once to
+ * `out_dtype`; the result is written to every one of the num_dsts (1..8)
+ * pointers of the HOST array `dsts` (this GPU's copy and, for an all-gather by
+ * peer stores, other GPUs'). rows * n a multiple of 8; 16-byte aligned
+ * pointers. No counterpart in the reference.
+ */
+KS_API ks_status_t ks_sum_parts(void* const* dsts, int num_dsts,
+                                const void* parts, int num_parts,
+                                int64_t rows, int64_t n,
+                                ks_dtype_t part_dtype, ks_dtype_t out_dtype,
+                                ks_stream_t stream);
+
 KS_END_EXTERN_C
 
 #endif /* KERNEL_SET_GEMM_H_ */

@@ -166,6 +166,9 @@ _decl("ks_gemm_fp8", _SCALED + [c_int64, c_int64, c_int64, c_int, c_int, c_int, 
 _decl("ks_gemm_w8a8", _SCALED + [_VP, c_int64, c_int64, c_int64, c_int, c_int, c_int, _VP])
 _decl("ks_gemm_fp8_blockwise_colscale", [_VP, _VP, _VP, POINTER(c_float), c_int64, POINTER(c_float), c_int64, c_int64,
                                         c_int64, c_int, c_int, c_int, _VP])
+_decl("ks_gemm_fp8_blockwise_scatter", [POINTER(_VP), c_int, c_int64, _VP, _VP, POINTER(c_float), POINTER(c_float),
+                                       c_int64, c_int64, c_int64, c_int, c_int, c_int, _VP])
+_decl("ks_sum_parts", [POINTER(_VP), c_int, _VP, c_int, c_int64, c_int64, c_int, c_int, _VP])
 _decl("ks_gemm_fp8_blockwise", _FP8_BW)
 _decl("ks_gemm_fp8_blockwise_nt", _FP8_BW)
 

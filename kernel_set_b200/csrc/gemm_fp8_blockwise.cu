@@ -235,4 +235,41 @@ ks_status_t ks_gemm_fp8_blockwise_colscale(void* out, const void* a_fp8, const v
   return sm100::launch_fp8_blockwise(a, as_stream(stream));
 }
 
+ks_status_t ks_gemm_fp8_blockwise_scatter(void* const* out_parts, int num_parts, int64_t rows_per_part,
+                                          const void* a_fp8, const void* b_fp8, const float* a_scale,
+                                          const float* b_scale, int64_t m, int64_t n, int64_t k, int b_layout,
+                                          ks_dtype_t fp8_dtype, ks_dtype_t out_dtype, ks_stream_t stream) {
+  using namespace ksb;
+  const char* where = "ks_gemm_fp8_blockwise_scatter";
+  KSB_REQUIRE_PTR(out_parts);
+  if (num_parts < 1 || num_parts > 8)
+    KSB_FAIL(KS_ERROR_INVALID_ARGUMENT, std::string(where) + ": between 1 and 8 output parts");
+  for (int i = 0; i < num_parts; ++i)
+    if (out_parts[i] == nullptr) KSB_FAIL(KS_ERROR_INVALID_ARGUMENT, std::string(where) + ": null output part");
+  if (b_layout != 0 && b_layout != 1)
+    KSB_FAIL(KS_ERROR_INVALID_ARGUMENT, std::string(where) + ": b_layout must be 0 ([K,N]) or 1 ([N,K])");
+  ks_status_t st = check_common(where, out_parts[0], a_fp8, b_fp8, a_scale, b_scale, m, n, k, 128, 128, fp8_dtype,
+                                out_dtype, false);
+  if (st != KS_SUCCESS) return st;
+  if (rows_per_part <= 0 || rows_per_part % 128 != 0 || rows_per_part * num_parts != m)
+    KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE,
+             std::string(where) + ": rows_per_part must be a multiple of 128 and num_parts * rows_per_part = m");
+  st = require_sm100(where);
+  if (st != KS_SUCCESS) return st;
+  st = poll_kernel_fault(where);
+  if (st != KS_SUCCESS) return st;
+  sm100::Fp8GemmArgs a;
+  a.where = where; a.out = nullptr; a.a = a_fp8; a.b = b_fp8; a.a_scale = a_scale;
+  a.b_scale = b_scale; a.m = m; a.n = n; a.k = k; a.nt = b_layout == 1;
+  a.e5m2 = fp8_dtype == KS_DTYPE_F8E5M2; a.out_dtype = out_dtype;
+  a.out_parts = out_parts; a.num_out_parts = num_parts; a.rows_per_part = rows_per_part;
+  const EnvChoice env = env_choice();
+  a.force_bn = env.bn;
+  a.force_split = 0;
+  if (!sm100::fp8_blockwise_eligible(a))
+    KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE,
+             std::string(where) + ": needs K (and N for [K,N]) multiples of 16 and 16-byte aligned operands");
+  return sm100::launch_fp8_blockwise(a, as_stream(stream));
+}
+
 }  // extern "C"

@@ -18,7 +18,6 @@
 #include <cstdlib>
 
 #include "common.cuh"
-#include "sm100_host.cuh"
 #include "kernel_set/quant.h"
 #include "quant_math.cuh"
 
@@ -74,10 +73,6 @@ template <typename T, bool E5M2, int kSegs>
 __global__ void __launch_bounds__(256)
 quant_group128_kernel(uint8_t* __restrict__ out, float* __restrict__ scale,
                       const T* __restrict__ in, int64_t total_groups, float qmax) {
-  // Programmatic dependent launch: the next kernel may start its prologue; this one waits for
-  // the kernel before it, whose output the input may be and which may still read `out`.
-  asm volatile("griddepcontrol.launch_dependents;");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   // a block owns kSegs consecutive runs of 256 segments (contiguous in memory)
   const int64_t stride = blockDim.x;
   const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x * kSegs + threadIdx.x;
@@ -158,9 +153,7 @@ void launch(uint8_t* out, float* scale, const T* in, int64_t rows, int64_t cols,
     if (quant_stream_blocks_per_sm() > 0 && blocks > 2 * resident) {
       quant_group128_stream_kernel<T, E5M2><<<static_cast<unsigned>(resident), 256, 0, s>>>(out, scale, in, total_groups, qmax);
     } else {
-      // (the launch status is picked up by the caller's cudaGetLastError)
-      sm100::launch_programmatic(quant_group128_kernel<T, E5M2, kSegs>, static_cast<unsigned>(blocks), 256u, 0, s, out, scale,
-                                 in, total_groups, qmax);
+      quant_group128_kernel<T, E5M2, kSegs><<<static_cast<unsigned>(blocks), 256, 0, s>>>(out, scale, in, total_groups, qmax);
     }
   } else {
     const int64_t warps = rows * groups_per_row;

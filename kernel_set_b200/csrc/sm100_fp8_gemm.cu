@@ -144,6 +144,15 @@ struct Params {
   // grouped, masked layout: expert e owns rows [e * max_m, e * max_m + masked_m[e])
   const int32_t* masked_m;
   int max_m;
+  // scattered output (dense, TMA-store epilogue only): rows [b * rows_per_part, (b + 1) *
+  // rows_per_part) leave through output tensor map b, as rows 0.. of that map; 0 = one output
+  int rows_per_part;
+};
+
+// Output tensor maps: one, or one per destination of a scattered output.
+constexpr int kMaxOutParts = 8;
+struct OutMaps {
+  CUtensorMap m[kMaxOutParts];
 };
 
 struct TileCoord {
@@ -236,7 +245,7 @@ static_assert(128 * Cfg<256>::kRegsIssue + (Cfg<256>::kThreads - 128) * Cfg<256>
 template <int BN, bool NT, bool GROUPED, typename OutT, int MODE = 0>
 __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
 fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                          const __grid_constant__ CUtensorMap tm_c, const Params p) {
+                          const __grid_constant__ OutMaps tm_cs, const Params p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -260,12 +269,6 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
   const int lane = threadIdx.x & 31;
   const WaitCtx wctx{abort_flag, p.fault_word};
 
-  // Programmatic dependent launch: the next kernel on the stream may start its prologue now;
-  // this one reads what the kernel before it may have produced (quantised activations and
-  // their scales, expert offsets) and writes its outputs only behind grid_dependency_wait():
-  // in the producer warp, in the epilogue warps and, for grouped problems, before the
-  // offsets are read.
-  grid_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
@@ -279,14 +282,13 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     fence_barrier_init();
     prefetch_tensormap(&tm_a);
     prefetch_tensormap(&tm_b);
-    if (!GROUPED && p.tma_store) prefetch_tensormap(&tm_c);
+    if (!GROUPED && p.tma_store) prefetch_tensormap(&tm_cs.m[0]);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
     tmem_relinquish();
   }
   if constexpr (GROUPED) {
-    grid_dependency_wait();
     // offs[e] = first row of expert e; with the masked layout the rows of an expert end at
     // offs[e] + masked_m[e] instead of at offs[e + 1] (ends[] holds either)
     int* ends = offs + (kMaxExperts + 1);
@@ -322,7 +324,6 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if constexpr (C::kRebalanceRegs) setmaxnreg_dec<C::kRegsIssue>();
-    grid_dependency_wait();
     uint32_t it = 0;
     bool ok = true;
     TileCoord tc;
@@ -398,7 +399,6 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
   } else if (warp >= 4) {
     // -------------------------------- epilogue --------------------------------
     if constexpr (C::kRebalanceRegs) setmaxnreg_inc<C::kRegsEpi>();
-    grid_dependency_wait();
     const int quarter = warp & 3;         // TMEM lane quarter this warp can address
     const int slice = (warp - 4) >> 2;    // which kEpiCols-wide column slice of the tile
     constexpr int EC = C::kEpiCols;
@@ -547,6 +547,10 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
           constexpr int kChunkCols = 16 / static_cast<int>(sizeof(OutT));
           const uint32_t my_stage = staging + (warp - 4) * C::kStoreStageBytes;
           const int store_row = tc.row0 + quarter * 32;
+          // a tile lies inside one part: rows_per_part is a multiple of the tile height
+          const int part_of_tile = p.rows_per_part > 0 ? tc.row0 / p.rows_per_part : 0;
+          const int part_row = store_row - part_of_tile * p.rows_per_part;
+          const CUtensorMap* out_map = &tm_cs.m[part_of_tile];
 #pragma unroll
           for (int pc = 0; pc < EC / kPieceCols; ++pc) {
             const int pcol = col0 + pc * kPieceCols;
@@ -561,7 +565,7 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_2d(&tm_c, my_stage, pcol, store_row);
+              tma_store_2d(out_map, my_stage, pcol, part_row);
               bulk_commit_group();
             }
           }
@@ -614,8 +618,6 @@ split_reduce_kernel(OutT* __restrict__ out, const float4* __restrict__ slots, in
   constexpr int EC = C::kEpiCols;
   constexpr int kChunks = EC / 4;
   constexpr int kPerTile = C::kEpiWarps * kChunks * 32;   // float4 per (tile, part)
-  grid_launch_dependents();
-  grid_dependency_wait();   // the parts are the GEMM kernel's output
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= tails * kPerTile) return;
   const int tail = idx / kPerTile;
@@ -687,28 +689,45 @@ ks_status_t launch_one(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUte
   }
   // Output tensor map for the TMA-store epilogue (dense problems whose rows keep
   // 16-byte alignment); otherwise the kernel stores from registers.
-  CUtensorMap tm_c = tm_a;
+  OutMaps tm_cs;
+  for (int i = 0; i < kMaxOutParts; ++i) tm_cs.m[i] = tm_a;
   p.tma_store = 0;
+  p.rows_per_part = 0;
   if (!GROUPED && p.vec_store) {
-    const uint64_t dims[2] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m)};
-    const uint64_t str[1] = {static_cast<uint64_t>(a.n) * sizeof(OutT)};
-    const uint32_t box[2] = {static_cast<uint32_t>(128 / sizeof(OutT)), 32u};
     const CUtensorMapDataType dt = std::is_same<OutT, float>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : std::is_same<OutT, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                                        : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    if (tma_encode(&tm_c, dt, 2, a.out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) p.tma_store = 1;
+    const uint64_t str[1] = {static_cast<uint64_t>(a.n) * sizeof(OutT)};
+    const uint32_t box[2] = {static_cast<uint32_t>(128 / sizeof(OutT)), 32u};
+    if (a.num_out_parts > 0) {
+      // every part is a [rows_per_part, n] matrix of its own (possibly in another GPU's memory)
+      bool ok = true;
+      for (int i = 0; i < a.num_out_parts && ok; ++i) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.rows_per_part)};
+        ok = tma_encode(&tm_cs.m[i], dt, 2, a.out_parts[i], dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+      }
+      if (ok) {
+        p.tma_store = 1;
+        p.rows_per_part = static_cast<int>(a.rows_per_part);
+      }
+    } else {
+      const uint64_t dims[2] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m)};
+      if (tma_encode(&tm_cs.m[0], dt, 2, a.out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) p.tma_store = 1;
+    }
   }
-  cudaError_t le = launch_programmatic(kernel, static_cast<unsigned>(grid), C::kThreads, C::smem_bytes(GROUPED), stream,
-                                       tm_a, tm_b, tm_c, p);
-  if (le != cudaSuccess) return cuda_status(le, a.where);
+  if (a.num_out_parts > 0 && !p.tma_store)
+    KSB_FAIL(KS_ERROR_UNSUPPORTED_SHAPE, std::string(a.where) + ": the scattered output needs 16-byte aligned rows and parts");
+  // (Programmatic dependent launch was measured on the quantizer -> GEMM -> reducer chain and
+  // lost 1 % there: these kernels have no input-independent prologue worth overlapping, and
+  // the dependency wait costs more than an ordinary kernel boundary.)
+  kernel<<<grid, C::kThreads, C::smem_bytes(GROUPED), stream>>>(tm_a, tm_b, tm_cs, p);
   if constexpr (!GROUPED) {
     if (p.split_s > 1) {
       const int tails = p.split_items / p.split_s;
       const int work = tails * C::kEpiWarps * (C::kEpiCols / 4) * 32;
-      le = launch_programmatic(split_reduce_kernel<BN, OutT>, static_cast<unsigned>((work + 255) / 256), 256u, 0, stream,
-                               static_cast<OutT*>(p.out), static_cast<const float4*>(p.split_slots), p.split_from,
-                               p.split_s, tails, p.tiles_m, p.tiles_n, p.m, p.n, p.vec_store);
-      if (le != cudaSuccess) return cuda_status(le, a.where);
+      split_reduce_kernel<BN, OutT><<<(work + 255) / 256, 256, 0, stream>>>(
+          static_cast<OutT*>(p.out), p.split_slots, p.split_from, p.split_s, tails, p.tiles_m, p.tiles_n, p.m, p.n,
+          p.vec_store);
     }
   }
   return cuda_status(cudaGetLastError(), a.where);
@@ -815,7 +834,9 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
   const uint32_t fmt = a.mode == 2 ? 1u : (a.e5m2 ? 1u : 0u);
   p.idesc = umma_instr_desc(fmt, fmt, 0u, a.nt ? 0u : 1u, kBM, static_cast<uint32_t>(bn), a.mode == 2 ? 2u : 1u);
   const size_t out_elt = a.out_dtype == KS_DTYPE_F32 ? 4 : 2;
-  p.vec_store = (aligned16(a.out) && (static_cast<size_t>(a.n) * out_elt) % 16 == 0) ? 1 : 0;
+  bool out_aligned = a.num_out_parts > 0 ? true : aligned16(a.out);
+  for (int i = 0; i < a.num_out_parts; ++i) out_aligned = out_aligned && aligned16(a.out_parts[i]);
+  p.vec_store = (out_aligned && (static_cast<size_t>(a.n) * out_elt) % 16 == 0) ? 1 : 0;
 
   int64_t tiles = tiles_m_bound * p.tiles_n;
   const int grid = static_cast<int>(tiles < sms ? (tiles < 1 ? 1 : tiles) : sms);
@@ -828,7 +849,7 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
   p.split_items = 0;
   p.split_s = 1;
   p.split_slots = nullptr;
-  if (!grouped && a.mode == 0 && a.force_split != 0 && tiles > grid) {
+  if (!grouped && a.mode == 0 && a.force_split != 0 && a.num_out_parts == 0 && tiles > grid) {
     const int rem = static_cast<int>(tiles % grid);
     int s = rem > 0 ? grid / rem : 1;
     if (s > 8) s = 8;

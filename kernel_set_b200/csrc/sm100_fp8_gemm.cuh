@@ -37,6 +37,13 @@ struct Fp8GemmArgs {
   int mode = 0;
   bool a_per_row = false, b_per_col = false;
   const void* bias = nullptr;
+  // Scattered output (dense, mode 0): rows [b * rows_per_part, (b + 1) * rows_per_part) of the
+  // product are written to out_parts[b] as a [rows_per_part, n] matrix; `out` is not used.
+  // rows_per_part is a multiple of 128 and m = num_out_parts * rows_per_part. The parts may
+  // live in other GPUs' memory (peer-mapped addresses): the tiles leave by TMA stores.
+  void* const* out_parts = nullptr;
+  int num_out_parts = 0;
+  int64_t rows_per_part = 0;
 };
 
 // True when the tcgen05 kernel can take the problem (128 x 128 scale blocks,

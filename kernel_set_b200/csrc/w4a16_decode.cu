@@ -502,15 +502,25 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
   if (n_pub > 0) {
     __threadfence();
     __syncwarp();
+    // both arrivals go out before either answer is needed (an atomic's round trip is ~1 us)
+    int tls[2], parts_of[2];
+    unsigned int prevs[2] = {0u, 0u};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tls[r] = r == 0 ? pub_tile[0] : pub_tile[1];
+      parts_of[r] = 0;
+      if (r < n_pub) {
+        const long long tile_u0 = static_cast<long long>(tls[r]) * p.k_steps;
+        const int first_cta = cta_of_unit(units, ctas, tile_u0);
+        parts_of[r] = cta_of_unit(units, ctas, tile_u0 + p.k_steps - 1) - first_cta + 1;
+        if (lane == 0) prevs[r] = atomicAdd(p.counters + tls[r] * kWarps + warp, 1u);
+      }
+    }
 #pragma unroll 1
     for (int r = 0; r < n_pub; ++r) {
-      const int tl = r == 0 ? pub_tile[0] : pub_tile[1];
-      const long long tile_u0 = static_cast<long long>(tl) * p.k_steps;
-      const int first_cta = cta_of_unit(units, ctas, tile_u0);
-      const int parts = cta_of_unit(units, ctas, tile_u0 + p.k_steps - 1) - first_cta + 1;
-      unsigned int prev = 0u;
-      if (lane == 0) prev = atomicAdd(p.counters + tl * kWarps + warp, 1u);
-      prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
+      const int tl = r == 0 ? tls[0] : tls[1];
+      const int parts = r == 0 ? parts_of[0] : parts_of[1];
+      const unsigned int prev = __shfl_sync(0xFFFFFFFFu, r == 0 ? prevs[0] : prevs[1], 0);
       if (prev != static_cast<unsigned int>(parts - 1)) continue;
       if (lane == 0) p.counters[tl * kWarps + warp] = 0u;   // ready for the next launch
       __threadfence();
@@ -521,14 +531,29 @@ __global__ void __launch_bounds__(kThreads, Cfg<MG>::kCtasPerSm) w4a16_decode_ke
         for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int j = 0; j < 4; ++j) acc[t][c][j] = 0.f;
-      for (int qd = 0; qd < parts; ++qd) {
-        const float* src = tile_slots + qd * part_stride;
+      // parts are added in part order; the loads of kAhead parts are in flight together
+      constexpr int kAhead = MG == 1 ? 4 : (MG == 2 ? 2 : 1);
+      for (int qd = 0; qd < parts; qd += kAhead) {
+        float v[kAhead][MG][2][4];
 #pragma unroll
-        for (int t = 0; t < MG; ++t)
+        for (int h = 0; h < kAhead; ++h) {
+          const float* src = tile_slots + (qd + h) * part_stride;
 #pragma unroll
-          for (int c = 0; c < 2; ++c)
+          for (int t = 0; t < MG; ++t)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[t][c][j] += __ldcg(src + ((t * 2 + c) * 4 + j) * 32);
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                v[h][t][c][j] = qd + h < parts ? __ldcg(src + ((t * 2 + c) * 4 + j) * 32) : 0.f;
+        }
+#pragma unroll
+        for (int h = 0; h < kAhead; ++h)
+#pragma unroll
+          for (int t = 0; t < MG; ++t)
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+              for (int j = 0; j < 4; ++j) acc[t][c][j] += v[h][t][c][j];
       }
       store_c(acc, tl);
     }

@@ -125,3 +125,44 @@ def gemm_fp8_blockwise_colscale(out: TensorLike, a_fp8: TensorLike, b_fp8: Tenso
                                              1 if b_layout == "nk" else 0, int(fp8_dtype), odt,
                                              default_stream(stream, a_fp8)), "ks_gemm_fp8_blockwise_colscale")
     return out
+
+
+def _ptr_array(items, name):
+    import ctypes
+    arr = (ctypes.c_void_p * len(items))()
+    for i, t in enumerate(items):
+        arr[i] = ptr(t, name=f"{name}[{i}]", allow_none=False)
+    return arr
+
+
+def gemm_fp8_blockwise_scatter(out_parts, a_fp8: TensorLike, b_fp8: TensorLike, a_scale: TensorLike,
+                               b_scale: TensorLike, m: int, n: int, k: int, rows_per_part: int,
+                               fp8_dtype: int = None, out_dtype: int = None, stream: TensorLike = None,
+                               b_layout: str = "kn"):
+    """The block-scaled GEMM whose row block ``b`` (``rows_per_part`` rows) is written to
+    ``out_parts[b]``, a ``[rows_per_part, n]`` tensor (or raw address) that may live in
+    another GPU's memory; see :func:`kernel_set_b200.parallel.FusedRowParallel`."""
+    if fp8_dtype is None:
+        fp8_dtype = infer_dtype(a_fp8, None)
+    odt = _out_dtype(out_parts[0], out_dtype, "ks_gemm_fp8_blockwise_scatter")
+    if b_layout not in ("kn", "nk"):
+        raise ValueError("b_layout must be 'kn' or 'nk'")
+    arr = _ptr_array(out_parts, "out_parts")
+    check(lib.ks_gemm_fp8_blockwise_scatter(arr, len(out_parts), int(rows_per_part), ptr(a_fp8, name="a_fp8"),
+                                            ptr(b_fp8, name="b_fp8"), f32_ptr(a_scale, name="a_scale"),
+                                            f32_ptr(b_scale, name="b_scale"), int(m), int(n), int(k),
+                                            1 if b_layout == "nk" else 0, int(fp8_dtype), odt,
+                                            default_stream(stream, a_fp8)), "ks_gemm_fp8_blockwise_scatter")
+    return out_parts
+
+
+def sum_parts(dsts, parts: TensorLike, num_parts: int, rows: int, n: int, part_dtype: int = None,
+              out_dtype: int = None, stream: TensorLike = None):
+    """``sum(parts[q] for q)`` in fp32, rounded once, written to every tensor (or raw
+    address) of ``dsts``; ``parts`` is ``[num_parts, rows, n]``."""
+    pdt = infer_dtype(parts, part_dtype)
+    odt = _out_dtype(dsts[0], out_dtype, "ks_sum_parts")
+    arr = _ptr_array(dsts, "dsts")
+    check(lib.ks_sum_parts(arr, len(dsts), ptr(parts, name="parts"), int(num_parts), int(rows), int(n), pdt, odt,
+                           default_stream(stream, parts)), "ks_sum_parts")
+    return dsts

@@ -196,6 +196,63 @@ def row_parallel_linear(x_shard: torch.Tensor, w8_kshard: torch.Tensor, ws_kshar
     return all_reduce_partials(partial, group)
 
 
+class FusedRowParallel:
+    """Row-parallel linear whose all-reduce runs inside the GEMM and one summing kernel, over
+    peer memory, instead of as a collective behind the GEMM.
+
+    Rank ``r`` owns the output rows ``[r * m / g, (r + 1) * m / g)``. Every rank's GEMM writes
+    its partial product of row block ``b`` straight into rank ``b``'s memory (TMA stores of
+    the finished tiles, ``ks_gemm_fp8_blockwise_scatter``), so the reduce-scatter's traffic
+    crosses NVLink while later tiles are still being computed. After a barrier each rank adds
+    the ``g`` slots of its rows in rank order in fp32 (``ks_sum_parts``: the same bits on
+    every run, and one rounding instead of the ``g`` of a bf16 all-reduce) and writes the
+    result into every rank's output buffer, which is the all-gather. A second barrier ends
+    the step. Buffers come from ``torch.distributed._symmetric_memory``.
+
+    The returned tensor is owned by this object and is overwritten by the next call.
+    """
+
+    def __init__(self, m: int, n: int, group=None, part_dtype=torch.float32, device=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if m % (BLOCK * self.world) != 0:
+            raise ValueError("m must be a multiple of 128 * world size")
+        self.m, self.n, self.rows = m, n, m // self.world
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.parts = symm_mem.empty((self.world, self.rows, n), dtype=part_dtype, device=device)
+        self.final = symm_mem.empty((m, n), dtype=torch.bfloat16, device=device)
+        self.h_parts = symm_mem.rendezvous(self.parts, self.group)
+        self.h_final = symm_mem.rendezvous(self.final, self.group)
+        slot = self.rows * n
+        # where this rank's partial of row block b goes: slot `rank` of rank b's parts
+        self.part_ptrs = [int(self.h_parts.buffer_ptrs[b]) + self.rank * slot * self.parts.element_size()
+                          for b in range(self.world)]
+        # where this rank's finished rows go in every rank's output
+        self.final_ptrs = [int(self.h_final.buffer_ptrs[b]) + self.rank * slot * 2 for b in range(self.world)]
+
+    def __call__(self, x_shard: torch.Tensor, w8_kshard: torch.Tensor, ws_kshard: torch.Tensor, ops=None,
+                 gather: bool = True) -> torch.Tensor:
+        from . import gemm
+        from ._tensor import dtype_to_ks
+        ops = ops or LibraryOps()
+        a8, a_s = ops.quant(x_shard, BLOCK)
+        return self.multiply(a8, a_s, w8_kshard, ws_kshard, gather)
+
+    def multiply(self, a8, a_s, w8_kshard, ws_kshard, gather: bool = True) -> torch.Tensor:
+        from . import gemm
+        from ._tensor import dtype_to_ks
+        k_local = a8.shape[1]
+        gemm.gemm_fp8_blockwise_scatter(self.part_ptrs, a8, w8_kshard, a_s, ws_kshard, self.m, self.n, k_local,
+                                        self.rows, out_dtype=dtype_to_ks(self.parts.dtype), b_layout="nk")
+        self.h_parts.barrier()   # every rank's slot of my rows has landed
+        dsts = self.final_ptrs if gather else [self.final_ptrs[self.rank]]
+        gemm.sum_parts(dsts, self.parts, self.world, self.rows, self.n, out_dtype=dtype_to_ks(torch.bfloat16))
+        self.h_final.barrier()   # every rank's rows have landed in my output; nobody reads parts any more
+        return self.final if gather else self.final[self.rank * self.rows:(self.rank + 1) * self.rows]
+
+
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     """silu(gate) * up for a [rows, 2*I] tensor holding gate then up."""
     i = gate_up.shape[1] // 2

@@ -33,7 +33,7 @@ def test_headers_compile_as_c_and_cpp(tmp_path):
 
 def test_every_declared_symbol_is_exported(ks):
     decl = declared_symbols()
-    assert len(decl) == 44, decl
+    assert len(decl) == 46, decl
     out = subprocess.run(["nm", "-D", "--defined-only", ks.LIB_PATH], capture_output=True, text=True, check=True)
     exported = sorted(l.split()[-1] for l in out.stdout.splitlines() if " T " in l)
     assert [s for s in decl if s not in exported] == []
@@ -146,6 +146,17 @@ def test_argument_validation_codes(ks):
     assert gc(ONE, ONE, ONE, 1, 8, D.F16, None) == S.INVALID_ARGUMENT        # out aliases input
     assert gc(P(32), ONE, ONE, 1, 8, D.I8, None) == S.UNSUPPORTED_DTYPE
     assert gc(P(32), ONE, ONE, 70000, 8, D.F16, None) == S.UNSUPPORTED_SHAPE
+    # scattered GEMM output and the sum of K-split parts
+    import ctypes
+    two = (ctypes.c_void_p * 2)(16, 32)
+    sc, sp = L.ks_gemm_fp8_blockwise_scatter, L.ks_sum_parts
+    assert sc(None, 2, 128, ONE, ONE, f32p(ONE), f32p(ONE), 256, 128, 128, 1, D.F8E4M3, D.BF16, None) == S.INVALID_ARGUMENT
+    assert sc(two, 9, 128, ONE, ONE, f32p(ONE), f32p(ONE), 256, 128, 128, 1, D.F8E4M3, D.BF16, None) == S.INVALID_ARGUMENT
+    assert sc(two, 2, 100, ONE, ONE, f32p(ONE), f32p(ONE), 200, 128, 128, 1, D.F8E4M3, D.BF16, None) == S.UNSUPPORTED_SHAPE
+    assert sc(two, 2, 128, ONE, ONE, f32p(ONE), f32p(ONE), 384, 128, 128, 1, D.F8E4M3, D.BF16, None) == S.UNSUPPORTED_SHAPE
+    assert sp(two, 0, ONE, 2, 8, 8, D.F32, D.BF16, None) == S.INVALID_ARGUMENT
+    assert sp(two, 2, ONE, 2, 8, 8, D.I8, D.BF16, None) == S.UNSUPPORTED_DTYPE
+    assert sp(two, 2, ONE, 2, 3, 3, D.F32, D.BF16, None) == S.UNSUPPORTED_SHAPE
     # ks_moe_grouped_gemm (reference moe_grouped_gemm.cu:140-153)
     gg = L.ks_moe_grouped_gemm
     assert gg(ONE, ONE, ONE, i32p(None), 2, 8, 8, 8, D.BF16, None) == S.INVALID_ARGUMENT

@@ -68,6 +68,23 @@ def _nccl_worker(rank, world, port, q):
         torch.cuda.synchronize()
         full32 = orc.fp8_gemm_blockwise(a8, w8, a_s, ws, layout="nk", out_dtype=None)
         frob_row = orc.rel_frobenius(out.float().cpu(), full32)
+        # the same layer with the all-reduce fused into the GEMM over peer memory (fp32 slots,
+        # summed in rank order): bf16 rounding of the fp32 sum, identical on both ranks and
+        # from call to call
+        xf, w8f, wsf = make_linear(256, 512, 2048, 3)
+        a8f, a_sf = orc.quantize_fp8_group(xf, 128)
+        _, _, bf_sh, bsf_sh, _ = par.shard_k(a8f, a_sf, w8f, wsf, rank, world, "nk")
+        fused = par.FusedRowParallel(256, 512, device=dev)
+        xs = xf[:, lo:hi].contiguous().to(dev)
+        out_f = fused(xs, bf_sh.to(dev), bsf_sh.to(dev)).clone()
+        out_f2 = fused(xs, bf_sh.to(dev), bsf_sh.to(dev)).clone()
+        torch.cuda.synchronize()
+        fullf = orc.fp8_gemm_blockwise(a8f, w8f, a_sf, wsf, layout="nk", out_dtype=None)
+        frob_fused = orc.rel_frobenius(out_f.float().cpu(), fullf.to(torch.bfloat16).float())
+        same = bool(torch.equal(out_f, out_f2))
+        gathered = [torch.empty_like(out_f) for _ in range(world)]
+        dist.all_gather(gathered, out_f)
+        same = same and all(bool(torch.equal(g, out_f)) for g in gathered)
         # expert-parallel MoE: tokens and experts both split, fp8 rows through all_to_all
         xm, ids, w, w1, s1, w2, s2 = make_moe(64, 256, 128, 8, 2, 3)
         t = 64 // world
@@ -79,7 +96,7 @@ def _nccl_worker(rank, world, port, q):
         torch.cuda.synchronize()
         ref = dense_moe_reference(xm, ids, w, w1, s1, w2, s2)[t_lo:t_hi]
         frob_moe = orc.rel_frobenius(got.float().cpu(), ref.float())
-        q.put((rank, float(frob_row), float(frob_moe)))
+        q.put((rank, float(frob_row), float(frob_moe), float(frob_fused), same))
     finally:
         dist.destroy_process_group()
 
@@ -102,7 +119,45 @@ def test_nccl_world2_row_parallel_and_expert_parallel(ks, cuda):
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for rank, frob_row, frob_moe in results:
+    for rank, frob_row, frob_moe, frob_fused, same in results:
         # two bf16 partials rounded before the sum and once after: a few 1e-3 at most
         assert frob_row < 4e-3, (rank, frob_row)
         assert frob_moe < 4e-3, (rank, frob_moe)
+        # fp32 slots: only the order of the fp32 additions differs from the unsplit product, which
+        # flips the final bf16 rounding of a few outputs
+        assert frob_fused < 1e-4, (rank, frob_fused)
+        assert same, "fused row-parallel output differs between calls or between ranks"
+
+
+def test_scattered_gemm_output_equals_plain(ks, cuda):
+    """ks_gemm_fp8_blockwise_scatter into four local buffers: row block b of the plain GEMM,
+    bit for bit, in bf16 and in fp32."""
+    g = torch.Generator(device=cuda).manual_seed(5)
+    m, n, k = 1024, 768, 1024
+    a = torch.randn(m, k, generator=g, device=cuda).to(torch.bfloat16)
+    w = torch.randn(n, k, generator=g, device=cuda) * 0.02
+    from _util import block_quant_nk_device
+    b8, b_s = block_quant_nk_device(w)
+    a8, a_s = ks.dispatch.per_token_group_quant(a)
+    for dt in (torch.bfloat16, torch.float32):
+        plain = torch.empty(m, n, dtype=dt, device=cuda)
+        ks.gemm.gemm_fp8_blockwise(plain, a8, b8, a_s, b_s, m, n, k, b_layout="nk")
+        parts = [torch.full((m // 4, n), -7.0, dtype=dt, device=cuda) for _ in range(4)]
+        ks.gemm.gemm_fp8_blockwise_scatter(parts, a8, b8, a_s, b_s, m, n, k, m // 4, b_layout="nk")
+        torch.cuda.synchronize()
+        for b in range(4):
+            assert torch.equal(parts[b], plain[b * (m // 4):(b + 1) * (m // 4)]), (dt, b)
+    with pytest.raises(ks.KernelSetError):
+        ks.gemm.gemm_fp8_blockwise_scatter(parts[:3], a8, b8, a_s, b_s, m, n, k, m // 4, b_layout="nk")
+
+
+@pytest.mark.parametrize("part_dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_sum_parts(ks, cuda, part_dtype):
+    g = torch.Generator(device=cuda).manual_seed(6)
+    parts = torch.randn(3, 40, 200, generator=g, device=cuda).to(part_dtype)
+    want32 = (parts[0].float() + parts[1].float()) + parts[2].float()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        dsts = [torch.empty(40, 200, dtype=out_dtype, device=cuda) for _ in range(2)]
+        ks.gemm.sum_parts(dsts, parts, 3, 40, 200)
+        torch.cuda.synchronize()
+        assert torch.equal(dsts[0], want32.to(out_dtype)) and torch.equal(dsts[1], dsts[0])
