@@ -3,9 +3,16 @@
 // block finds its (expert, row tile) from the offsets itself, where the
 // reference builds a schedule with a one-thread kernel into a buffer it
 // allocates and frees around a stream synchronisation.
+//
+// f16 / bf16 problems with 16-byte row pitches run on the tcgen05 mainloop of the FP8 GEMM
+// (its 16-bit mode: kind::f16, the whole K range accumulated in tensor memory); the
+// environment variable KS_B200_GROUPED_PATH=general pins the SIMT kernel (tests).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm_general.cuh"
 #include "kernel_set/moe.h"
+#include "sm100_fp8_gemm.cuh"
 
 namespace ksb {
 namespace {
@@ -40,6 +47,20 @@ extern "C" ks_status_t ks_moe_grouped_gemm(void* c, const void* a, const void* b
   ks_status_t st = require_sm100(where);
   if (st != KS_SUCCESS) return st;
   cudaStream_t s = as_stream(stream);
+  if (dtype == KS_DTYPE_F16 || dtype == KS_DTYPE_BF16) {
+    static const bool reload = std::getenv("KS_B200_ENV_RELOAD") != nullptr;
+    static const bool general_cached = [] { const char* v = std::getenv("KS_B200_GROUPED_PATH"); return v && v[0] == 'g'; }();
+    bool pin_general = general_cached;
+    if (reload) { const char* v = std::getenv("KS_B200_GROUPED_PATH"); pin_general = v && v[0] == 'g'; }
+    sm100::Fp8GemmArgs g;
+    g.where = where; g.out = c; g.a = a; g.b = b; g.offsets = expert_offsets; g.num_experts = num_experts;
+    g.m = total_rows; g.n = n; g.k = k; g.nt = false; g.out_dtype = dtype; g.mode = 3;
+    if (!pin_general && sm100::fp8_blockwise_eligible(g)) {
+      st = poll_kernel_fault(where);
+      if (st != KS_SUCCESS) return st;
+      return sm100::launch_fp8_blockwise(g, s);
+    }
+  }
   switch (dtype) {
     case KS_DTYPE_F32: launch<float>(c, a, b, expert_offsets, num_experts, total_rows, n, k, s); break;
     case KS_DTYPE_F16: launch<__half>(c, a, b, expert_offsets, num_experts, total_rows, n, k, s); break;

@@ -30,16 +30,6 @@ namespace {
 
 using namespace quantmath;
 
-// Blocks per SM of the grid-stride kernel; 0 selects the one-segment-per-thread kernel
-// (KS_B200_QUANT_STREAM, read once; tests and profiling only).
-int quant_stream_blocks_per_sm() {
-  static const int v = [] {
-    const char* e = std::getenv("KS_B200_QUANT_STREAM");
-    return e ? std::atoi(e) : 0;
-  }();
-  return v;
-}
-
 // A thread owns kSegs segments, all loaded before the first is used. Measured on B200 for
 // [4096, 7168] bf16: 22 us with one segment per thread, 25 us with two, 35 us with four
 // (fewer resident threads cost more than the extra loads in flight gain), so one it is.
@@ -93,29 +83,6 @@ quant_group128_kernel(uint8_t* __restrict__ out, float* __restrict__ scale,
   for (int s = 0; s < kSegs; ++s) quant_segment<T, E5M2>(out, scale, v[s], first + s * stride, live[s], qmax);
 }
 
-// Grid-stride form of the same kernel: a thread walks over segments first, first + stride, ...
-// and has the next segment's 32 bytes on their way while it works on the current one, so a
-// thread never sits in its arithmetic with nothing in flight.
-template <typename T, bool E5M2>
-__global__ void __launch_bounds__(256)
-quant_group128_stream_kernel(uint8_t* __restrict__ out, float* __restrict__ scale,
-                             const T* __restrict__ in, int64_t total_groups, float qmax) {
-  const int64_t total_segs = total_groups * 8;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  int64_t seg = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t warp_first = seg - (threadIdx.x & 31);
-  Raw16<T> next = seg < total_segs ? Raw16<T>::load(in + seg * 16) : Raw16<T>::zero();
-  // all lanes of a warp leave the loop together (the shuffles inside need them)
-  for (int64_t base = warp_first; base < total_segs; base += stride, seg += stride) {
-    const Raw16<T> cur = next;
-    const int64_t nseg = seg + stride;
-    next = nseg < total_segs ? Raw16<T>::load(in + nseg * 16) : Raw16<T>::zero();
-    float v[16];
-    cur.unpack(v);
-    quant_segment<T, E5M2>(out, scale, v, seg, seg < total_segs, qmax);
-  }
-}
-
 // Any group size, any width, any alignment: one warp per (row, group).
 template <typename T, bool E5M2>
 __global__ void __launch_bounds__(256)
@@ -149,12 +116,9 @@ void launch(uint8_t* out, float* scale, const T* in, int64_t rows, int64_t cols,
     const int64_t total_groups = rows * groups_per_row;
     constexpr int kSegs = KSB_QUANT_SEGS;
     const int64_t blocks = (total_groups * 8 + 256 * kSegs - 1) / (256 * kSegs);
-    const int64_t resident = static_cast<int64_t>(sm_count()) * quant_stream_blocks_per_sm();
-    if (quant_stream_blocks_per_sm() > 0 && blocks > 2 * resident) {
-      quant_group128_stream_kernel<T, E5M2><<<static_cast<unsigned>(resident), 256, 0, s>>>(out, scale, in, total_groups, qmax);
-    } else {
-      quant_group128_kernel<T, E5M2, kSegs><<<static_cast<unsigned>(blocks), 256, 0, s>>>(out, scale, in, total_groups, qmax);
-    }
+    // (a grid-stride form with the next segment's loads in flight during the arithmetic was
+    // measured at the same 22-24 us and is not kept)
+    quant_group128_kernel<T, E5M2, kSegs><<<static_cast<unsigned>(blocks), 256, 0, s>>>(out, scale, in, total_groups, qmax);
   } else {
     const int64_t warps = rows * groups_per_row;
     const int64_t blocks = (warps + 7) / 8;

@@ -242,6 +242,8 @@ static_assert(128 * Cfg<256>::kRegsIssue + (Cfg<256>::kThreads - 128) * Cfg<256>
 // MODE 1: FP8 with one scale per row of A and one per column of B: the whole K range
 //         accumulates in tensor memory, the epilogue runs once per tile.
 // MODE 2: the same with int8 operands (kind::i8, int32 accumulators) and an optional bias.
+// MODE 3: f16 / bf16 operands (kind::f16), no scales: a K-block is 64 elements (the same 128
+//         bytes per row), B stored [K,N] is loaded in 64-column atoms. The unscaled grouped GEMM.
 template <int BN, bool NT, bool GROUPED, typename OutT, int MODE = 0>
 __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1)
 fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -340,6 +342,11 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
           tma_load_2d_elect(a_dst, &tm_a, full, kb * kBK, tc.row0);
           if constexpr (NT) {
             tma_load_3d_elect(b_dst, &tm_b, full, kb * kBK, tc.n0, tc.expert);
+          } else if constexpr (MODE == 3) {
+            // the map sees B as bytes: 64 columns of 16 bits = one 128-byte atom, 64 k-rows per K-block
+#pragma unroll
+            for (int h = 0; h < BN / 64; ++h)
+              tma_load_3d_elect(b_dst + h * (64 * 128), &tm_b, full, 2 * tc.n0 + h * 128, kb * 64, tc.expert);
           } else {
 #pragma unroll
             for (int h = 0; h < BN / 128; ++h)
@@ -382,10 +389,14 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
             // 128-column atoms 16 KB apart, 8-k groups 1024 B apart, a K step of 32
             // rows is 32 * 128 B.
             const uint64_t a_desc = umma_smem_desc_sw128(a_src + kk * 32, 16, 1024);
+            // (16-bit operands, MODE 3: the same bytes per instruction, 16 elements; an MN-major
+            // atom is 64 columns x 64 k-rows = 8 KB and a K step of 16 rows is 16 * 128 B)
             const uint64_t b_desc = NT ? umma_smem_desc_sw128(b_src + kk * 32, 16, 1024)
-                                       : umma_smem_desc_sw128(b_src + kk * 32 * 128, 128 * kBK, 1024);
+                                    : MODE == 3 ? umma_smem_desc_sw128(b_src + kk * 16 * 128, 64 * 128, 1024)
+                                                : umma_smem_desc_sw128(b_src + kk * 32 * 128, 128 * kBK, 1024);
             const uint32_t accumulate = (kk > 0 || (MODE != 0 && kb > tc.kb0)) ? 1u : 0u;
             if constexpr (MODE == 2) umma_i8_elect(d_tmem, a_desc, b_desc, p.idesc, accumulate);
+            else if constexpr (MODE == 3) umma_f16_elect(d_tmem, a_desc, b_desc, p.idesc, accumulate);
             else umma_f8f6f4_elect(d_tmem, a_desc, b_desc, p.idesc, accumulate);
           }
           tc_commit_elect(bar_empty + 8 * s);
@@ -414,9 +425,10 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
       const int col0 = tc.n0 + slice * EC;
       int nb = col0 >> 7;
       if (nb > p.nnb - 1) nb = p.nnb - 1;
-      const float* as_ptr = p.a_scale + static_cast<size_t>(row_ok ? row : 0) * p.as_row_stride;
-      const float* bs_ptr = p.b_scale + static_cast<size_t>(tc.expert) * p.nkb * p.nnb +
-                            (NT ? static_cast<size_t>(nb) * p.nkb : static_cast<size_t>(nb));
+      const float* as_ptr = MODE == 3 ? nullptr : p.a_scale + static_cast<size_t>(row_ok ? row : 0) * p.as_row_stride;
+      const float* bs_ptr = MODE == 3 ? nullptr
+                                      : p.b_scale + static_cast<size_t>(tc.expert) * p.nkb * p.nnb +
+                                            (NT ? static_cast<size_t>(nb) * p.nkb : static_cast<size_t>(nb));
       const size_t bs_step = NT ? 1 : static_cast<size_t>(p.nnb);
 
       float2 acc[EC / 2];
@@ -431,8 +443,11 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
         ++tile_n;
         if (!mbar_wait_long(wctx, bar_accfull + 8 * tbuf, tph, 0x400u + tbuf)) { ok = false; break; }
         tc_fence_after_sync();
-        const float a_sc = (p.a_per_row && row_ok) ? __ldg(p.a_scale + row) : __ldg(p.a_scale);
-        const float b_one = __ldg(p.b_scale);
+        float a_sc = 1.f, b_one = 1.f;
+        if constexpr (MODE != 3) {
+          a_sc = (p.a_per_row && row_ok) ? __ldg(p.a_scale + row) : __ldg(p.a_scale);
+          b_one = __ldg(p.b_scale);
+        }
         const OutT* bias = static_cast<const OutT*>(p.bias);
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tbuf * BN + slice * EC;
 #pragma unroll
@@ -449,10 +464,13 @@ fp8_blockwise_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
           for (int j = 0; j < 16; ++j) {
             const int col = col0 + c * 16 + j;
             const bool col_ok = col < p.n;
-            const float b_sc = (p.b_per_col && col_ok) ? __ldg(p.b_scale + col) : b_one;
             const float raw = MODE == 2 ? static_cast<float>(static_cast<int32_t>(r[j])) : __uint_as_float(r[j]);
-            float v = __fmul_rn(__fmul_rn(raw, a_sc), b_sc);
-            if (bias != nullptr && col_ok) v = __fadd_rn(v, to_f32<OutT>(bias[col]));
+            float v = raw;
+            if constexpr (MODE != 3) {
+              const float b_sc = (p.b_per_col && col_ok) ? __ldg(p.b_scale + col) : b_one;
+              v = __fmul_rn(__fmul_rn(raw, a_sc), b_sc);
+              if (bias != nullptr && col_ok) v = __fadd_rn(v, to_f32<OutT>(bias[col]));
+            }
             if (j & 1) acc[c * 8 + (j >> 1)].y = v; else acc[c * 8 + (j >> 1)].x = v;
           }
         }
@@ -750,6 +768,14 @@ ks_status_t launch_bn(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUten
   // the per-row / per-column scaled kernels exist for the reference's layout (B stored [K,N]), dense
   if (a.mode == 1) return launch_out<BN, false, false, 1>(a, tm_a, tm_b, p, grid, stream);
   if (a.mode == 2) return launch_out<BN, false, false, 2>(a, tm_a, tm_b, p, grid, stream);
+  // 16-bit operands, B stored [K,N]: the output has the operands' type
+  if (a.mode == 3) {
+    if (a.out_dtype == KS_DTYPE_F16)
+      return grouped ? launch_one<BN, false, true, __half, 3>(a, tm_a, tm_b, p, grid, stream)
+                     : launch_one<BN, false, false, __half, 3>(a, tm_a, tm_b, p, grid, stream);
+    return grouped ? launch_one<BN, false, true, __nv_bfloat16, 3>(a, tm_a, tm_b, p, grid, stream)
+                   : launch_one<BN, false, false, __nv_bfloat16, 3>(a, tm_a, tm_b, p, grid, stream);
+  }
   if (a.nt) return grouped ? launch_out<BN, true, true>(a, tm_a, tm_b, p, grid, stream)
                            : launch_out<BN, true, false>(a, tm_a, tm_b, p, grid, stream);
   return grouped ? launch_out<BN, false, true>(a, tm_a, tm_b, p, grid, stream)
@@ -760,9 +786,15 @@ ks_status_t launch_bn(const Fp8GemmArgs& a, const CUtensorMap& tm_a, const CUten
 
 bool fp8_blockwise_eligible(const Fp8GemmArgs& a) {
   if (a.mode == 0 && (a.block_n != 128 || a.block_k != 128)) return false;
-  if (a.mode != 0 && (a.nt || a.offsets != nullptr || a.masked_m != nullptr)) return false;
-  if (a.k % 16 != 0) return false;
-  if (!a.nt && a.n % 16 != 0) return false;
+  if ((a.mode == 1 || a.mode == 2) && (a.nt || a.offsets != nullptr || a.masked_m != nullptr)) return false;
+  if (a.mode == 3) {
+    // 16-bit operands: 16-byte row pitches of A [M,K] and B [K,N]
+    if (a.nt || a.masked_m != nullptr || a.k % 8 != 0 || a.n % 8 != 0) return false;
+    if (a.out_dtype != KS_DTYPE_F16 && a.out_dtype != KS_DTYPE_BF16) return false;
+  } else {
+    if (a.k % 16 != 0) return false;
+    if (!a.nt && a.n % 16 != 0) return false;
+  }
   if (!aligned16(a.a) || !aligned16(a.b)) return false;
   if (a.m > INT32_MAX / 2 || a.n > INT32_MAX / 2 || a.k > INT32_MAX / 2) return false;
   if ((a.offsets != nullptr || a.masked_m != nullptr) && (a.num_experts > kMaxExperts || a.num_experts < 1)) return false;
@@ -787,6 +819,20 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
   const int bn = (a.force_bn == 128 || a.force_bn == 256) ? a.force_bn : (cost256 <= cost128 ? 256 : 128);
 
   CUtensorMap tm_a, tm_b;
+  // 16-bit operands (mode 3) are described to TMA as bytes: a row of A is 2K bytes, of B 2N
+  const int64_t k_bytes = a.mode == 3 ? 2 * a.k : a.k;
+  if (a.mode == 3) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k_bytes), static_cast<uint64_t>(a.m)};
+    const uint64_t str[1] = {static_cast<uint64_t>(k_bytes)};
+    const uint32_t box[2] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(kBM)};
+    if (!encode_u8(&tm_a, a.a, 2, dims, str, box))
+      KSB_FAIL(KS_ERROR_INTERNAL, std::string(a.where) + ": tensor map for A rejected");
+    const uint64_t bdims[3] = {static_cast<uint64_t>(2 * a.n), static_cast<uint64_t>(a.k), static_cast<uint64_t>(experts)};
+    const uint64_t bstr[2] = {static_cast<uint64_t>(2 * a.n), static_cast<uint64_t>(2 * a.n) * static_cast<uint64_t>(a.k)};
+    const uint32_t bbox[3] = {128u, 64u, 1u};
+    if (!encode_u8(&tm_b, a.b, 3, bdims, bstr, bbox))
+      KSB_FAIL(KS_ERROR_INTERNAL, std::string(a.where) + ": tensor map for B rejected");
+  } else {
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(a.m)};
     const uint64_t str[1] = {static_cast<uint64_t>(a.k)};
@@ -807,6 +853,7 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
     if (!encode_u8(&tm_b, a.b, 3, dims, str, box))
       KSB_FAIL(KS_ERROR_INTERNAL, std::string(a.where) + ": tensor map for B rejected");
   }
+  }
 
   Params p;
   p.out = a.out;
@@ -825,13 +872,14 @@ ks_status_t launch_fp8_blockwise(const Fp8GemmArgs& a, cudaStream_t stream) {
   p.m = static_cast<int>(a.m);
   p.n = static_cast<int>(a.n);
   p.k = static_cast<int>(a.k);
-  p.nkb = static_cast<int>((a.k + kBK - 1) / kBK);
+  p.nkb = static_cast<int>((k_bytes + kBK - 1) / kBK);
   p.nnb = static_cast<int>((a.n + 127) / 128);
   p.tiles_n = static_cast<int>((a.n + bn - 1) / bn);
   p.tiles_m = static_cast<int>((a.m + kBM - 1) / kBM);
   // operand formats: e4m3 / e5m2 for the fp8 kinds; signed 8-bit integers with an int32
   // accumulator for kind::i8
-  const uint32_t fmt = a.mode == 2 ? 1u : (a.e5m2 ? 1u : 0u);
+  // (kind::f16: 0 = f16, 1 = bf16)
+  const uint32_t fmt = a.mode == 2 ? 1u : (a.mode == 3 ? (a.out_dtype == KS_DTYPE_BF16 ? 1u : 0u) : (a.e5m2 ? 1u : 0u));
   p.idesc = umma_instr_desc(fmt, fmt, 0u, a.nt ? 0u : 1u, kBM, static_cast<uint32_t>(bn), a.mode == 2 ? 2u : 1u);
   const size_t out_elt = a.out_dtype == KS_DTYPE_F32 ? 4 : 2;
   bool out_aligned = a.num_out_parts > 0 ? true : aligned16(a.out);

@@ -33,7 +33,8 @@ struct Fp8GemmArgs {
   int64_t max_m = 0;
   // mode 0: block scales as above. mode 1: fp8 operands, a_scale [m] or [1], b_scale [n] or
   // [1] (kernels/src/gemm/gemm_fp8.cu of the reference). mode 2: int8 operands, same scales,
-  // optional bias [n] in the output type (gemm_w8a8.cu).
+  // optional bias [n] in the output type (gemm_w8a8.cu). mode 3: f16 / bf16 operands of type
+  // out_dtype, a [m, k], b [E][k, n], no scales (kernels/src/moe/moe_grouped_gemm.cu), dense or grouped.
   int mode = 0;
   bool a_per_row = false, b_per_col = false;
   const void* bias = nullptr;

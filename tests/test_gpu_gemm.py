@@ -438,6 +438,48 @@ def test_grouped_gemm_plain(ks, cuda, dtype):
         assert orc.rel_frobenius(out2.float(), from_bits16(g2["out"], dtype).float()) < 3e-3
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,n,k", [
+    ([130, 0, 257, 1, 128, 64, 0, 300], 512, 1024),     # ragged experts, several row tiles each
+    ([17, 200, 3], 264, 200),                            # N and K with partial tiles (multiples of 8 only)
+    ([128] * 32, 2048, 768),                             # more tiles than SMs
+])
+def test_grouped_gemm_plain_tensor_core(ks, cuda, dtype, rows, n, k):
+    """f16 / bf16 grouped GEMM on the tcgen05 mainloop (16-bit mode) against the oracle with the
+    usual GEMM bound, and against the SIMT kernel."""
+    offs = ragged_offsets(rows)
+    total, e = int(offs[-1]), len(rows)
+    g = gen(total + n + k)
+    a = torch.randn(total, k, generator=g).to(dtype)
+    b = (torch.randn(e, k, n, generator=g) * 0.05).to(dtype)
+    args = (a.to(cuda), b.to(cuda), offs.to(cuda))
+    out = ks.dispatch.moe(*args, num_experts=e, n=n, k=k)
+    out2 = ks.dispatch.moe(*args, num_experts=e, n=n, k=k)
+    torch.cuda.synchronize()
+    ks.runtime.stream_synchronize(0)
+    ref32 = orc.grouped_gemm(a, b, offs.tolist(), out_dtype=None)
+    noise = torch.zeros_like(ref32)
+    for i in range(e):
+        lo, hi = int(offs[i]), int(offs[i + 1])
+        if hi > lo:
+            noise[lo:hi] = accumulation_noise(a[lo:hi].float().abs(), b[i].float().abs(), k)
+    if dtype == torch.bfloat16:
+        check_gemm(out.cpu(), ref32, noise, f"grouped {dtype} {total}x{n}x{k}")
+    assert orc.rel_frobenius(out.cpu().float(), ref32) < 3e-3
+    assert torch.equal(out, out2)
+    old = os.environ.get("KS_B200_GROUPED_PATH")
+    os.environ["KS_B200_GROUPED_PATH"] = "general"
+    try:
+        simt = ks.dispatch.moe(*args, num_experts=e, n=n, k=k)
+        torch.cuda.synchronize()
+    finally:
+        if old is None:
+            os.environ.pop("KS_B200_GROUPED_PATH", None)
+        else:
+            os.environ["KS_B200_GROUPED_PATH"] = old
+    assert orc.rel_frobenius(out.cpu().float(), simt.cpu().float()) < 3e-3
+
+
 def test_grouped_gemm_plain_fp8_operands(ks, cuda):
     """fp8 dtype: raw code values multiplied, C written in the same fp8 type."""
     offs = ragged_offsets([3, 20])
