@@ -862,9 +862,10 @@ def main():
                          "frac": achieved / fp8_peak,
                          # dram__bytes_read.sum + dram__bytes_write.sum per launch of this kernel on this
                          # workload, from one ncu capture (algorithmic bytes: 140.4e6)
-                         "traffic": 133.4e6 if (world == 1 and m == M) else None,
-                         "traffic_source": "ncu capture of fp8_blockwise_umma_kernel on this workload, "
-                                           "dram__bytes_read.sum + dram__bytes_write.sum per launch",
+                         "traffic": 149.5e6 if (world == 1 and m == M) else None,
+                         "traffic_source": "one ncu capture (--set full) of fp8_blockwise_umma_kernel on this workload, "
+                                           "dram__bytes_read.sum (102.9 MB) + dram__bytes_write.sum (46.7 MB) per "
+                                           "launch; a constant from that capture, not a measurement of this run",
                          "kernel": "fp8_blockwise_umma_kernel", "us_per_launch": gemm_ms * 1e3,
                          "peak_source": f"2 x {peaks['source']} burst cuBLAS bf16 ({peaks['bf16_burst']} TFLOP/s): the "
                                         "timed region is milliseconds long; no FP8 figure was measured on this pool",

@@ -443,6 +443,7 @@ def test_grouped_gemm_plain(ks, cuda, dtype):
     ([130, 0, 257, 1, 128, 64, 0, 300], 512, 1024),     # ragged experts, several row tiles each
     ([17, 200, 3], 264, 200),                            # N and K with partial tiles (multiples of 8 only)
     ([128] * 32, 2048, 768),                             # more tiles than SMs
+    ([200] * 24 + [520, 129], 2048, 512),                # several row tiles per expert
 ])
 def test_grouped_gemm_plain_tensor_core(ks, cuda, dtype, rows, n, k):
     """f16 / bf16 grouped GEMM on the tcgen05 mainloop (16-bit mode) against the oracle with the
