@@ -58,6 +58,8 @@
 #include <cstdio>
 #include <mutex>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "sm100_host.cuh"
 #include "sm100_ptx.cuh"
@@ -909,6 +911,12 @@ ks_status_t launch_w4a16(const W4A16Args& a, cudaStream_t stream) {
   unsigned int* counters = static_cast<unsigned int*>(stream_scratch(stream, counter_bytes, 1));
   if (slots == nullptr || counters == nullptr)
     KSB_FAIL(KS_ERROR_OUT_OF_MEMORY, "ks_gemm_w4a16: workspace allocation failed");
+  if (std::getenv("KS_B200_ENV_RELOAD") != nullptr && std::getenv("KS_B200_TEST_DIRTY_COUNTERS") != nullptr) {
+    // test hook: what a launch that gave up half-way leaves behind, without any GPU fault:
+    // garbage in the counters and the mark that the fault poll would have set
+    cudaMemsetAsync(counters, 0xFF, stream_scratch_bytes(stream, 1), stream);
+    stream_scratch_mark_dirty(1);
+  }
   if (stream_scratch_take_dirty(stream, 1)) {
     cudaError_t e = cudaMemsetAsync(counters, 0, stream_scratch_bytes(stream, 1), stream);
     if (e != cudaSuccess) return cuda_status(e, "ks_gemm_w4a16: clearing the split-K counters");

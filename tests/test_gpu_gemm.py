@@ -306,6 +306,36 @@ def test_w4a16_decode_kernel(ks, cuda, m, k, n, gs, dtype, zeros, bias):
     assert orc.rel_frobenius(out.cpu().float(), gen_out.cpu().float()) < 2e-3
 
 
+@pytest.mark.parametrize("path", ["decode", "tcgen05"])
+def test_w4a16_recovers_from_dirty_split_counters(ks, cuda, path):
+    """A launch that gives up on a bounded wait can leave split-K arrival counters non-zero; the
+    fault poll marks every stream's counters and the next call clears them. Staged here without
+    any GPU fault: a test hook fills the counters with garbage and sets the same mark."""
+    m, k, n, gs = 8, 4096, 512, 128           # every column tile is shared by several CTAs
+    g = gen(77)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    codes = torch.randint(0, 16, (k, n), generator=g).to(torch.int32)
+    scales = (torch.randn(k // gs, n, generator=g).mul(0.02).abs() + 1e-3).to(torch.bfloat16)
+    zp = torch.full((k // gs, n), 8.0).to(torch.bfloat16)
+    b_packed = orc.pack_int4_bytes(codes)
+    args = (a.to(cuda), b_packed.to(cuda), scales.to(cuda), zp.to(cuda))
+    with w4_path(path):
+        clean = ks.dispatch.w4a16(*args, group_size=gs)
+        torch.cuda.synchronize()
+        os.environ["KS_B200_TEST_DIRTY_COUNTERS"] = "1"
+        try:
+            after = ks.dispatch.w4a16(*args, group_size=gs)
+            torch.cuda.synchronize()
+        finally:
+            os.environ.pop("KS_B200_TEST_DIRTY_COUNTERS", None)
+        again = ks.dispatch.w4a16(*args, group_size=gs)
+        torch.cuda.synchronize()
+        ks.runtime.stream_synchronize(0)
+    assert torch.equal(clean, after) and torch.equal(clean, again)
+    ref32 = orc.w4a16(a, b_packed, scales, zp, gs, None, out_dtype=None)
+    assert orc.rel_frobenius(clean.cpu().float(), ref32) < 3e-3
+
+
 @pytest.mark.parametrize("k,n", [(4096, 28672), (14336, 4096)])
 def test_w4a16_baseline_shapes(ks, cuda, k, n):
     """The decode sweep of the benchmark (Llama-3-8B MLP shapes, M in {1, 8, 32, 128}), default
