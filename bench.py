@@ -650,6 +650,25 @@ def run_cfg4(args, torch, dist, ks, parallel, dev, rank, world):
 
     steps = max(3, min(args.steps, 10))
     ms_step = timed(step, steps, 2, barrier, torch)
+    # the same layer with dispatch and combine as peer stores (FusedExpertParallel)
+    fused = None
+    if world > 1:
+        try:
+            layer = parallel.FusedExpertParallel(t_local, topk, hidden, inter, experts, device=dev)
+
+            def step_fused():
+                ks.moe.gate_softmax_topk(w_l, ids_l, logits_l, t_local, experts, topk, renormalize=True)
+                return layer(x_l, ids_l, w_l, w1, s1, w2, s2)
+
+            same = bool(torch.equal(step_fused(), step()))
+            ms_fused = timed(step_fused, steps, 2, barrier, torch)
+            tf = torch.tensor([ms_fused, 0.0 if same else 1.0], dtype=torch.float64, device=dev)
+            dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+            fused = {"ms_per_step": float(tf[0]), "equal_to_the_nccl_path_bit_for_bit": float(tf[1]) == 0.0}
+            del layer
+            torch.cuda.empty_cache()
+        except Exception as exc:   # symmetric memory not available on this machine
+            fused = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
     # the two grouped GEMMs alone, on the rows this rank's experts receive
     import ks_oracle as orc
     _, ids_all = orc.moe_route(logits, topk)
@@ -689,7 +708,7 @@ def run_cfg4(args, torch, dist, ks, parallel, dev, rank, world):
         "grouped_gemms_us": ms_gemm * 1e3, "other_us": (ms_step - ms_gemm) * 1e3,
         "grouped_gemms_tflops_per_gpu": flops / world / (ms_gemm * 1e-3) / 1e12,
         "grouped_gemms_weight_gbs": weight_bytes / (ms_gemm * 1e-3) / 1e9,
-        "parity": parity}
+        "parity": parity, "fused_over_peer_memory": fused}
 
 
 def main():

@@ -160,6 +160,57 @@ KS_API ks_status_t ks_moe_grouped_gemm_fp8_blockwise_masked(
     int b_layout, ks_dtype_t fp8_dtype, ks_dtype_t out_dtype,
     ks_stream_t stream);
 
+/*
+ * Expert-parallel dispatch and combine through peer memory (no counterpart in the
+ * reference, which has no multi-GPU path). Experts are split contiguously over the
+ * ranks, `experts_per_rank` each (the last rank may own fewer). `counts` is the
+ * all-gathered matrix int32 [world, world * experts_per_rank]: counts[s][e] = rows
+ * rank s routes to expert e (0 for padding experts).
+ *
+ * ks_moe_dispatch_plan (one small kernel) derives, for the calling rank:
+ *   dst_base      [world * experts_per_rank]   row at which this rank's rows of expert e
+ *                                              start in the receive buffer of rank
+ *                                              e / experts_per_rank
+ *   local_offsets [experts_per_rank + 1]       expert offsets of the rows this rank receives
+ *                                              (expert-major, inside an expert by source)
+ *   seg_start     [experts_per_rank * world + 1]  first received row of (expert, source)
+ *   ret_base      [experts_per_rank * world]   position of that segment's first row in
+ *                                              the source rank's sorted order
+ */
+KS_API ks_status_t ks_moe_dispatch_plan(int32_t* dst_base, int32_t* local_offsets,
+                                        int32_t* seg_start, int32_t* ret_base,
+                                        const int32_t* counts, int world, int rank,
+                                        int experts_per_rank, ks_stream_t stream);
+
+/*
+ * ks_moe_permute_quant_fp8 with every output row written to its destination rank:
+ * sorted row r of expert e goes to row dst_base[e] + r - expert_offsets[e] of
+ * dst_fp8[e / experts_per_rank] ([capacity_rows, hidden] fp8) and its scales to the
+ * same row of dst_scale[...] ([capacity_rows, hidden / 128] f32). `dst_fp8` and
+ * `dst_scale` are HOST arrays of `world` device pointers (peer-mapped addresses; the
+ * entry of the calling rank is its own buffer). Rows outside [0, capacity_rows) are
+ * dropped. Codes and scales are those of ks_quantize_fp8_group(group_size = 128).
+ * The caller places a cross-rank barrier between this call and the use of the buffers.
+ */
+KS_API ks_status_t ks_moe_permute_quant_fp8_scatter(
+    void* const* dst_fp8, float* const* dst_scale, int world, int64_t capacity_rows,
+    const int32_t* dst_base, const int32_t* expert_offsets, int num_experts,
+    int experts_per_rank, const void* input, const int32_t* sorted_token_ids,
+    int64_t num_tokens, int top_k, int64_t hidden, ks_dtype_t in_dtype,
+    ks_dtype_t fp8_dtype, ks_stream_t stream);
+
+/*
+ * The way back: received row i (i < seg_start[segments], read on the device) of `src`
+ * ([capacity_rows, hidden] `dtype`) lies in segment j (seg_start[j] <= i) and is copied
+ * to row ret_base[j] + i - seg_start[j] of dst[j % world] ([dst_rows, hidden]).
+ * `dst` is a HOST array of `world` device pointers. segments = experts of this rank x world.
+ */
+KS_API ks_status_t ks_moe_scatter_rows(void* const* dst, int world, int64_t dst_rows,
+                                       const void* src, int64_t capacity_rows,
+                                       const int32_t* seg_start, const int32_t* ret_base,
+                                       int segments, int64_t hidden, ks_dtype_t dtype,
+                                       ks_stream_t stream);
+
 KS_END_EXTERN_C
 
 #endif /* KERNEL_SET_MOE_H_ */

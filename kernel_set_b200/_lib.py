@@ -187,6 +187,12 @@ _decl("ks_moe_compute_permutation", [POINTER(c_int32), POINTER(c_int32), POINTER
 _decl("ks_moe_permute", [_VP, _VP, POINTER(c_int32), c_int64, c_int, c_int64, c_int, _VP])
 _decl("ks_moe_permute_quant_fp8", [_VP, POINTER(c_float), _VP, POINTER(c_int32), c_int64, c_int, c_int64, c_int, c_int, _VP])
 _decl("ks_moe_unpermute", [_VP, _VP, POINTER(c_int32), POINTER(c_float), c_int64, c_int, c_int64, c_int, _VP])
+_decl("ks_moe_dispatch_plan", [POINTER(c_int32), POINTER(c_int32), POINTER(c_int32), POINTER(c_int32), POINTER(c_int32),
+                              c_int, c_int, c_int, _VP])
+_decl("ks_moe_permute_quant_fp8_scatter", [POINTER(_VP), POINTER(_VP), c_int, c_int64, POINTER(c_int32), POINTER(c_int32),
+                                          c_int, c_int, _VP, POINTER(c_int32), c_int64, c_int, c_int64, c_int, c_int, _VP])
+_decl("ks_moe_scatter_rows", [POINTER(_VP), c_int, c_int64, _VP, c_int64, POINTER(c_int32), POINTER(c_int32), c_int, c_int64,
+                             c_int, _VP])
 _decl("ks_moe_grouped_gemm", [_VP, _VP, _VP, POINTER(c_int32), c_int, c_int64, c_int64, c_int64, c_int, _VP])
 _decl("ks_moe_grouped_gemm_fp8_blockwise",
       [_VP, _VP, _VP, POINTER(c_float), POINTER(c_float), POINTER(c_int32), c_int, c_int64, c_int64, c_int64,

@@ -138,3 +138,54 @@ def grouped_gemm_fp8_blockwise_masked(out: TensorLike, a_fp8: TensorLike, b_fp8:
         int(num_experts), int(max_m), int(n), int(k), int(block_n), int(block_k), 1 if b_layout == "nk" else 0,
         int(fp8_dtype), int(out_dtype), default_stream(stream, a_fp8)), "ks_moe_grouped_gemm_fp8_blockwise_masked")
     return out
+
+
+def _ptr_array(items, name):
+    import ctypes
+    arr = (ctypes.c_void_p * len(items))()
+    for i, t in enumerate(items):
+        arr[i] = ptr(t, name=f"{name}[{i}]", allow_none=False)
+    return arr
+
+
+def dispatch_plan(dst_base: TensorLike, local_offsets: TensorLike, seg_start: TensorLike, ret_base: TensorLike,
+                  counts: TensorLike, world: int, rank: int, experts_per_rank: int, stream: TensorLike = None):
+    """From the all-gathered count matrix ``counts [world, world * experts_per_rank]`` int32:
+    where this rank's rows land on their destination ranks (``dst_base``), the expert offsets
+    of what it receives (``local_offsets``), and the (expert, source) segments with their way
+    back (``seg_start``, ``ret_base``). All int32, on the device."""
+    check(lib.ks_moe_dispatch_plan(i32_ptr(dst_base, name="dst_base"), i32_ptr(local_offsets, name="local_offsets"),
+                                   i32_ptr(seg_start, name="seg_start"), i32_ptr(ret_base, name="ret_base"),
+                                   i32_ptr(counts, name="counts"), int(world), int(rank), int(experts_per_rank),
+                                   default_stream(stream, counts)), "ks_moe_dispatch_plan")
+    return dst_base, local_offsets, seg_start, ret_base
+
+
+def permute_quant_fp8_scatter(dst_fp8, dst_scale, capacity_rows: int, dst_base: TensorLike, expert_offsets: TensorLike,
+                              num_experts: int, experts_per_rank: int, input: TensorLike,
+                              sorted_token_ids: TensorLike, num_tokens: int, top_k: int, hidden: int,
+                              in_dtype: Optional[int] = None, fp8_dtype: int = None, stream: TensorLike = None):
+    """:func:`permute_quant_fp8` with every row written to its destination rank's buffer
+    (``dst_fp8[d]`` / ``dst_scale[d]``: tensors or raw peer addresses) at its expert-major row."""
+    from .enums import DType
+    dt = infer_dtype(input, in_dtype)
+    q = _ptr_array(dst_fp8, "dst_fp8")
+    s = _ptr_array(dst_scale, "dst_scale")
+    check(lib.ks_moe_permute_quant_fp8_scatter(q, s, len(dst_fp8), int(capacity_rows), i32_ptr(dst_base, name="dst_base"),
+                                               i32_ptr(expert_offsets, name="expert_offsets"), int(num_experts),
+                                               int(experts_per_rank), ptr(input, name="input"),
+                                               i32_ptr(sorted_token_ids, name="sorted_token_ids"), int(num_tokens),
+                                               int(top_k), int(hidden), dt,
+                                               int(fp8_dtype if fp8_dtype is not None else DType.F8E4M3),
+                                               default_stream(stream, input)), "ks_moe_permute_quant_fp8_scatter")
+
+
+def scatter_rows(dst, dst_rows: int, src: TensorLike, capacity_rows: int, seg_start: TensorLike, ret_base: TensorLike,
+                 segments: int, hidden: int, dtype: Optional[int] = None, stream: TensorLike = None):
+    """Received row ``i`` of ``src`` goes back to row ``ret_base[j] + i - seg_start[j]`` of
+    ``dst[j % world]`` (tensors or raw peer addresses), ``j`` the segment that holds ``i``."""
+    dt = infer_dtype(src, dtype)
+    arr = _ptr_array(dst, "dst")
+    check(lib.ks_moe_scatter_rows(arr, len(dst), int(dst_rows), ptr(src, name="src"), int(capacity_rows),
+                                  i32_ptr(seg_start, name="seg_start"), i32_ptr(ret_base, name="ret_base"),
+                                  int(segments), int(hidden), dt, default_stream(stream, src)), "ks_moe_scatter_rows")

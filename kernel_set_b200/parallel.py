@@ -253,6 +253,92 @@ class FusedRowParallel:
         return self.final if gather else self.final[self.rank * self.rows:(self.rank + 1) * self.rows]
 
 
+class FusedExpertParallel:
+    """Expert-parallel MoE layer whose dispatch and combine are peer stores of the kernels that
+    produce the rows, instead of all-to-all collectives with a regrouping pass on either side.
+
+    Steps on every rank: counting-sort permutation; all-gather of the per-expert counts (small,
+    on the device); ``ks_moe_dispatch_plan``; gather + 1 x 128 quantizer writing every row into
+    its destination rank's buffer at its final expert-major position
+    (``ks_moe_permute_quant_fp8_scatter``); barrier; grouped GEMM, SwiGLU + quantizer, grouped
+    GEMM on the received buffer as it is; ``ks_moe_scatter_rows`` writes every result row back to
+    the position the source's unpermute expects; barrier; weighted unpermute. The only host read
+    (the number of received rows, for the row counts of the kernels in the middle) is issued
+    right after the plan and waited for after the first GEMM has been enqueued.
+
+    Buffers (``torch.distributed._symmetric_memory``) are sized for the worst case, every row of
+    every rank landing on one rank. The returned tensor is overwritten by the next call.
+    """
+
+    def __init__(self, tokens_per_rank: int, top_k: int, hidden: int, inter: int, num_experts: int, group=None,
+                 device=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.t_local, self.k, self.hidden, self.inter, self.num_experts = tokens_per_rank, top_k, hidden, inter, num_experts
+        self.per = -(-num_experts // self.world)
+        self.e_pad = self.per * self.world
+        self.e_local = max(0, min(self.per, num_experts - self.rank * self.per))
+        dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.dev = dev
+        self.pairs = tokens_per_rank * top_k
+        self.cap = self.pairs * self.world
+        self.recv_q = symm_mem.empty((self.cap, hidden), dtype=torch.uint8, device=dev)
+        self.recv_s = symm_mem.empty((self.cap, hidden // BLOCK), dtype=torch.float32, device=dev)
+        self.back = symm_mem.empty((self.pairs, hidden), dtype=torch.bfloat16, device=dev)
+        self.h_q = symm_mem.rendezvous(self.recv_q, self.group)
+        self.h_s = symm_mem.rendezvous(self.recv_s, self.group)
+        self.h_back = symm_mem.rendezvous(self.back, self.group)
+        self.q_ptrs = [int(p) for p in self.h_q.buffer_ptrs]
+        self.s_ptrs = [int(p) for p in self.h_s.buffer_ptrs]
+        self.back_ptrs = [int(p) for p in self.h_back.buffer_ptrs]
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.counts_all = torch.zeros(self.world, self.e_pad, **i32)
+        self.counts_mine = torch.zeros(self.e_pad, **i32)
+        self.dst_base = torch.zeros(self.e_pad, **i32)
+        self.local_offsets = torch.zeros(self.per + 1, **i32)
+        self.seg_start = torch.zeros(self.per * self.world + 1, **i32)
+        self.ret_base = torch.zeros(self.per * self.world, **i32)
+        self.total_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.total_ready = torch.cuda.Event()
+        # activations between the two GEMMs, worst case
+        self.h = torch.empty(self.cap, 2 * inter, dtype=torch.bfloat16, device=dev)
+        self.a8 = torch.empty(self.cap, inter, dtype=torch.float8_e4m3fn, device=dev)
+        self.a_s = torch.empty(self.cap, inter // BLOCK, dtype=torch.float32, device=dev)
+        self.y = torch.empty(self.cap, hidden, dtype=torch.bfloat16, device=dev)
+
+    def __call__(self, tokens, topk_ids, topk_weights, w1_8, w1_s, w2_8, w2_s, ops=None):
+        from . import activation, moe
+        ops = ops or LibraryOps()
+        k, hidden, inter = self.k, self.hidden, self.inter
+        ids32 = topk_ids.to(device=self.dev, dtype=torch.int32).contiguous()
+        weights = topk_weights.to(device=self.dev, dtype=torch.float32).contiguous()
+        sorted_ids, offsets = ops.permutation(ids32, self.num_experts)
+        self.counts_mine[:self.num_experts] = offsets[1:] - offsets[:-1]
+        dist.all_gather_into_tensor(self.counts_all, self.counts_mine, group=self.group)
+        moe.dispatch_plan(self.dst_base, self.local_offsets, self.seg_start, self.ret_base, self.counts_all,
+                          self.world, self.rank, self.per)
+        self.total_host.copy_(self.local_offsets[self.per:], non_blocking=True)
+        self.total_ready.record()
+        moe.permute_quant_fp8_scatter(self.q_ptrs, self.s_ptrs, self.cap, self.dst_base, offsets, self.num_experts,
+                                      self.per, tokens, sorted_ids, self.t_local, k, hidden)
+        self.h_q.barrier()    # every rank's rows (and scales) for my experts have landed
+        if self.e_local > 0:
+            moe.grouped_gemm_fp8_blockwise(self.h, self.recv_q.view(torch.float8_e4m3fn), w1_8, self.recv_s, w1_s,
+                                           self.local_offsets, self.e_local, self.cap, 2 * inter, hidden, b_layout="nk")
+        self.total_ready.synchronize()
+        total = int(self.total_host[0])
+        if self.e_local > 0 and total > 0:
+            activation.swiglu_packed_quant_fp8(self.a8, self.a_s, self.h, total, inter)
+            moe.grouped_gemm_fp8_blockwise(self.y, self.a8, w2_8, self.a_s, w2_s, self.local_offsets, self.e_local,
+                                           self.cap, hidden, inter, b_layout="nk")
+        moe.scatter_rows(self.back_ptrs, self.pairs, self.y, self.cap, self.seg_start, self.ret_base,
+                         self.per * self.world, hidden)
+        self.h_back.barrier()  # every expert's rows of my tokens are back
+        return ops.unpermute(self.back, sorted_ids, weights, self.t_local, k)
+
+
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     """silu(gate) * up for a [rows, 2*I] tensor holding gate then up."""
     i = gate_up.shape[1] // 2

@@ -33,7 +33,7 @@ def test_headers_compile_as_c_and_cpp(tmp_path):
 
 def test_every_declared_symbol_is_exported(ks):
     decl = declared_symbols()
-    assert len(decl) == 46, decl
+    assert len(decl) == 49, decl
     out = subprocess.run(["nm", "-D", "--defined-only", ks.LIB_PATH], capture_output=True, text=True, check=True)
     exported = sorted(l.split()[-1] for l in out.stdout.splitlines() if " T " in l)
     assert [s for s in decl if s not in exported] == []
@@ -157,6 +157,21 @@ def test_argument_validation_codes(ks):
     assert sp(two, 0, ONE, 2, 8, 8, D.F32, D.BF16, None) == S.INVALID_ARGUMENT
     assert sp(two, 2, ONE, 2, 8, 8, D.I8, D.BF16, None) == S.UNSUPPORTED_DTYPE
     assert sp(two, 2, ONE, 2, 3, 3, D.F32, D.BF16, None) == S.UNSUPPORTED_SHAPE
+    # expert-parallel dispatch / combine through peer memory
+    dp, pqs, sr = L.ks_moe_dispatch_plan, L.ks_moe_permute_quant_fp8_scatter, L.ks_moe_scatter_rows
+    assert dp(i32p(ONE), i32p(ONE), i32p(ONE), i32p(ONE), i32p(None), 2, 0, 4, None) == S.INVALID_ARGUMENT
+    assert dp(i32p(ONE), i32p(ONE), i32p(ONE), i32p(ONE), i32p(ONE), 9, 0, 4, None) == S.INVALID_ARGUMENT
+    assert dp(i32p(ONE), i32p(ONE), i32p(ONE), i32p(ONE), i32p(ONE), 2, 2, 4, None) == S.INVALID_ARGUMENT
+    assert dp(i32p(ONE), i32p(ONE), i32p(ONE), i32p(ONE), i32p(ONE), 8, 0, 200, None) == S.UNSUPPORTED_SHAPE
+    assert pqs(two, two, 2, 64, i32p(ONE), i32p(ONE), 8, 4, ONE, i32p(ONE), 4, 2, 100, D.BF16, D.F8E4M3, None) \
+        == S.UNSUPPORTED_SHAPE
+    assert pqs(two, two, 2, 64, i32p(ONE), i32p(ONE), 8, 2, ONE, i32p(ONE), 4, 2, 128, D.BF16, D.F8E4M3, None) \
+        == S.INVALID_ARGUMENT      # 8 experts, 2 per rank, but only 2 ranks
+    assert pqs(two, two, 2, 64, i32p(ONE), i32p(ONE), 8, 4, ONE, i32p(ONE), 4, 2, 128, D.I8, D.F8E4M3, None) \
+        == S.UNSUPPORTED_DTYPE
+    assert sr(two, 2, 8, ONE, 8, i32p(ONE), i32p(ONE), 3, 128, D.BF16, None) == S.INVALID_ARGUMENT   # 3 segments, 2 ranks
+    assert sr(two, 2, 8, ONE, 8, i32p(ONE), i32p(ONE), 4, 4, D.BF16, None) == S.UNSUPPORTED_SHAPE
+    assert sr(two, 2, 8, ONE, 8, i32p(ONE), i32p(ONE), 4, 128, D.I32, None) == S.UNSUPPORTED_DTYPE
     # ks_moe_grouped_gemm (reference moe_grouped_gemm.cu:140-153)
     gg = L.ks_moe_grouped_gemm
     assert gg(ONE, ONE, ONE, i32p(None), 2, 8, 8, 8, D.BF16, None) == S.INVALID_ARGUMENT

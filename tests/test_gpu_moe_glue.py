@@ -213,3 +213,69 @@ def test_swiglu_quant_equals_swiglu_then_quantize(ks, cuda, rows, inter, dtype):
     mismatch = (q.cpu().view(torch.uint8) != q_ref.view(torch.uint8)).float().mean().item()
     assert mismatch < 2e-3
     assert torch.allclose(s.cpu(), s_ref, rtol=1e-2)
+
+
+def test_peer_dispatch_and_combine_on_one_device(ks, cuda):
+    """The three steps of the peer-memory dispatch / combine with both "ranks" on one GPU (the
+    destination pointers are local tensors): every row must land, bit for bit, where the plan
+    says, and come back to the position of the source's sorted order."""
+    world, experts, per, tokens, k, hidden = 2, 6, 3, 40, 2, 256
+    g = gen(31)
+    pairs = tokens * k
+    cap = pairs * world
+    xs, sorted_ids, offsets, q_loc, s_loc = [], [], [], [], []
+    for r in range(world):
+        x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).to(cuda)
+        ids = torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(tokens)]).to(torch.int32).to(cuda)
+        sid = torch.empty(pairs, dtype=torch.int32, device=cuda)
+        off = torch.empty(experts + 1, dtype=torch.int32, device=cuda)
+        ks.moe.compute_permutation(sid, off, ids, tokens, experts, k)
+        q = torch.empty(pairs, hidden, dtype=torch.float8_e4m3fn, device=cuda)
+        s = torch.empty(pairs, hidden // 128, dtype=torch.float32, device=cuda)
+        ks.moe.permute_quant_fp8(q, s, x, sid, tokens, k, hidden)
+        xs.append(x); sorted_ids.append(sid); offsets.append(off); q_loc.append(q); s_loc.append(s)
+    counts = torch.stack([o[1:] - o[:-1] for o in offsets]).contiguous()        # [world, experts]
+    recv_q = [torch.full((cap, hidden), 0xAA, dtype=torch.uint8, device=cuda) for _ in range(world)]
+    recv_s = [torch.full((cap, hidden // 128), -1.0, device=cuda) for _ in range(world)]
+    plans = []
+    for r in range(world):
+        dst_base = torch.empty(experts, dtype=torch.int32, device=cuda)
+        local_off = torch.empty(per + 1, dtype=torch.int32, device=cuda)
+        seg_start = torch.empty(per * world + 1, dtype=torch.int32, device=cuda)
+        ret_base = torch.empty(per * world, dtype=torch.int32, device=cuda)
+        ks.moe.dispatch_plan(dst_base, local_off, seg_start, ret_base, counts, world, r, per)
+        plans.append((dst_base, local_off, seg_start, ret_base))
+        ks.moe.permute_quant_fp8_scatter(recv_q, recv_s, cap, dst_base, offsets[r], experts, per, xs[r], sorted_ids[r],
+                                         tokens, k, hidden)
+    torch.cuda.synchronize()
+    c = counts.cpu()
+    offs_h = [o.cpu() for o in offsets]
+    for d in range(world):
+        local_off = plans[d][1].cpu()
+        row = 0
+        for el in range(per):
+            e = d * per + el
+            assert int(local_off[el]) == row
+            for s in range(world):
+                n = int(c[s, e])
+                lo = int(offs_h[s][e])
+                assert torch.equal(recv_q[d][row:row + n], q_loc[s][lo:lo + n].view(torch.uint8)), (d, el, s)
+                assert torch.equal(recv_s[d][row:row + n], s_loc[s][lo:lo + n]), (d, el, s)
+                row += n
+        assert int(local_off[per]) == row
+        assert bool((recv_q[d][row:] == 0xAA).all()), "rows beyond the received ones were written"
+    # the way back
+    back = [torch.zeros(pairs, hidden, dtype=torch.bfloat16, device=cuda) for _ in range(world)]
+    ys = [torch.randn(cap, hidden, generator=g).to(torch.bfloat16).to(cuda) for _ in range(world)]
+    for d in range(world):
+        ks.moe.scatter_rows(back, pairs, ys[d], cap, plans[d][2], plans[d][3], per * world, hidden)
+    torch.cuda.synchronize()
+    for d in range(world):
+        row = 0
+        for el in range(per):
+            e = d * per + el
+            for s in range(world):
+                n = int(c[s, e])
+                lo = int(offs_h[s][e])
+                assert torch.equal(back[s][lo:lo + n], ys[d][row:row + n]), (d, el, s)
+                row += n

@@ -96,6 +96,15 @@ def _nccl_worker(rank, world, port, q):
         torch.cuda.synchronize()
         ref = dense_moe_reference(xm, ids, w, w1, s1, w2, s2)[t_lo:t_hi]
         frob_moe = orc.rel_frobenius(got.float().cpu(), ref.float())
+        # the same layer with dispatch and combine as peer stores: same kernels on the same rows in
+        # the same order, so the same bits; twice, to go through the buffers' reuse
+        layer = par.FusedExpertParallel(t, 2, 256, 128, 8, device=dev)
+        margs = (xm[t_lo:t_hi].to(dev), ids[t_lo:t_hi].to(dev), w[t_lo:t_hi].to(dev), w1[e_lo:e_hi].to(dev),
+                 s1[e_lo:e_hi].to(dev), w2[e_lo:e_hi].to(dev), s2[e_lo:e_hi].to(dev))
+        got_f = layer(*margs).clone()
+        got_f2 = layer(*margs).clone()
+        torch.cuda.synchronize()
+        same = same and bool(torch.equal(got_f, got)) and bool(torch.equal(got_f2, got))
         q.put((rank, float(frob_row), float(frob_moe), float(frob_fused), same))
     finally:
         dist.destroy_process_group()
@@ -126,7 +135,7 @@ def test_nccl_world2_row_parallel_and_expert_parallel(ks, cuda):
         # fp32 slots: only the order of the fp32 additions differs from the unsplit product, which
         # flips the final bf16 rounding of a few outputs
         assert frob_fused < 1e-4, (rank, frob_fused)
-        assert same, "fused row-parallel output differs between calls or between ranks"
+        assert same, "a fused (peer-memory) path differs between calls, between ranks or from the NCCL path"
 
 
 def test_scattered_gemm_output_equals_plain(ks, cuda):
