@@ -116,8 +116,11 @@ void launch(uint8_t* out, float* scale, const T* in, int64_t rows, int64_t cols,
     const int64_t total_groups = rows * groups_per_row;
     constexpr int kSegs = KSB_QUANT_SEGS;
     const int64_t blocks = (total_groups * 8 + 256 * kSegs - 1) / (256 * kSegs);
-    // (a grid-stride form with the next segment's loads in flight during the arithmetic was
-    // measured at the same 22-24 us and is not kept)
+    // (Measured and not kept: a grid-stride form with the next segment's loads in flight during
+    // the arithmetic, 22-24 us; persistent blocks fed by 8 KB bulk copies through a 12-stage
+    // shared-memory ring, ~190 KB in flight per SM: 5.4 TB/s on [16384, 7168] where this kernel
+    // reaches 5.6, and slower on [4096, 7168]. At that size a fixed ~5 us of launch, ramp and
+    // tail is what separates the kernel from its steady-state rate.)
     quant_group128_kernel<T, E5M2, kSegs><<<static_cast<unsigned>(blocks), 256, 0, s>>>(out, scale, in, total_groups, qmax);
   } else {
     const int64_t warps = rows * groups_per_row;

@@ -60,7 +60,8 @@ def test_rms_norm_quant_equals_norm_then_quantize(ks, cuda, rows, cols, dtype):
 
 
 @pytest.mark.parametrize("rows,cols,ld,dtype", [(4096, 7168, 4096, torch.bfloat16), (130, 256, 132, torch.float16),
-                                                (5, 128, 8, torch.float32)])
+                                                (5, 128, 8, torch.float32),
+                                                (1361, 7168, 1364, torch.float16)])
 def test_quantizer_column_major_scales(ks, cuda, rows, cols, ld, dtype):
     x = torch.randn(rows, cols, generator=gen(rows + cols + ld)).to(dtype).to(cuda)
     q = torch.empty(rows, cols, dtype=torch.float8_e4m3fn, device=cuda)

@@ -26,6 +26,7 @@ def run_quant(ks, x_cpu, gs, fp8, dev):
     (5, 700, 300, torch.float32, "e5m2"),       # group larger than a warp pass
     (1, 1, 128, torch.bfloat16, "e4m3"),
     (3, 129, 128, torch.bfloat16, "e4m3"),      # odd width: unaligned rows
+    (1361, 7168, 128, torch.float16, "e5m2"),   # several generations of blocks, a partly filled last one
 ])
 def test_quantizer_bit_exact(ks, cuda, rows, cols, gs, dtype, fp8):
     x = (torch.randn(rows, cols, generator=gen(rows * 131 + cols)) * 3.0).to(dtype)
@@ -95,6 +96,23 @@ def test_quantizer_bf16_patterns(ks, cuda):
     x = bits.to(torch.int32).to(torch.int16).view(torch.bfloat16).reshape(groups // 16, 16 * 128).contiguous()
     q_ref, s_ref = orc.quantize_fp8_group(x, 128)
     q, s = run_quant(ks, x, 128, "e4m3", cuda)
+    assert torch.equal(s, s_ref)
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+
+
+@pytest.mark.parametrize("fp8", ["e4m3", "e5m2"])
+def test_quantizer_every_bf16_maximum(ks, cuda, fp8):
+    """Every non-negative finite bf16 value as a group's maximum (32 640 groups): the scale is
+    amax / qmax for each of them, and the codes of a few fractions of it."""
+    bits = torch.arange(0, 0x7F80, dtype=torch.int32)
+    amax = bits.to(torch.int16).view(torch.bfloat16)
+    x = torch.zeros(bits.numel(), 128, dtype=torch.bfloat16)
+    x[:, 0] = amax
+    frac = torch.tensor([0.5, -0.75, 0.3, -0.11, 0.97, 1.0 / 3], dtype=torch.float32)
+    x[:, 1:7] = (amax.float()[:, None] * frac[None, :]).to(torch.bfloat16)
+    x = x.reshape(-1, 16 * 128).contiguous()
+    q_ref, s_ref = orc.quantize_fp8_group(x, 128, fp8)
+    q, s = run_quant(ks, x, 128, fp8, cuda)
     assert torch.equal(s, s_ref)
     assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
 
