@@ -33,13 +33,16 @@
 // tile inside the GEMM kernel measured 3-4 % gain instead of the 10 % the idle round costs:
 // one CTA then reads S x 128 KB behind a fence and four dependent atomics while its tensor
 // core waits.)
-// Measured on B200 (in-kernel cycle counters): a K-block of a 128 x 256 tile takes
-// ~850 cycles against 512 of tensor work. The epilogue's share is a serial chain per
-// warp (barrier test ~100, eight dependent TMEM loads ~55 each, 128 FMAs per thread:
-// the FP32 pipe alone needs 256 cycles per K-block) and with two accumulator buffers
-// the MMA warp and the epilogue take turns more than they overlap. Wider loads, more
-// loads in flight, sixteen narrower epilogue warps, 224-wide tiles, paced MMA issue
-// and sleeping or spinning waits were all measured and did not beat this arrangement.
+// Measured on B200 with work-skipping builds of this kernel (M=4096, N=K=7168; the full kernel
+// 201-204 us): MMAs and operand loads without any epilogue work 152 us (TMA writes 48 KB and
+// the MMAs read 48 KB of shared memory per K-block; MMAs alone, from resident shared memory,
+// 125 us); the epilogue alone 155 us, of which the eight TMEM loads per K-block are nearly
+// free and the 128 FMAs per thread cost ~540 cycles (two epilogue warps per scheduler), the
+// scale fetches ~10 %; barriers alone 58 us. The two sides are equally long and the two
+// accumulator buffers couple them instead of letting them overlap fully. Measured and not
+// better: handing the accumulator over in two 128-column halves (eight N=128 MMAs per
+// K-block read A twice: 232 us), wider loads, more loads in flight, sixteen narrower epilogue
+// warps, 224-wide tiles, scalar FMAs, paced MMA issue, sleeping or spinning waits.
 // B may be stored [N,K] (K-major UMMA operand) or [K,N] (MN-major operand, the
 // layout of the reference C ABI); both are loaded by TMA without a transpose.
 //
