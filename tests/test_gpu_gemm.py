@@ -528,9 +528,10 @@ def test_grouped_gemm_plain_fp8_operands(ks, cuda):
     ("nk", "tcgen05", 512, 384),
     ("kn", "tcgen05", 512, 384),
     ("nk", "tcgen05", 336, 400),
+    ("nk", "tcgen05", 200, 1040),
 ])
 def test_grouped_gemm_fp8_blockwise(ks, cuda, layout, path, n, k):
-    rows = [130, 0, 7, 256, 1, 129, 0, 64]
+    rows = [130, 0, 7, 256, 1, 129, 0, 64, 300, 16, 17, 513]
     e = len(rows)
     offs = ragged_offsets(rows)
     total = int(offs[-1])
