@@ -13,8 +13,9 @@
 // hand-offs lie between a packed byte arriving and its product being issued.
 // Feeding tcgen05.mma needs the dequantised operand in shared memory (2 x 32 KB
 // of shared-memory traffic per 8 KB of packed weight) or in tensor memory
-// (tcgen05.st at ~80 B/clk per SM plus two more barrier hops per unit). A
-// register-operand mma.sync takes the dequantised pairs where they are made.
+// (tcgen05.st, 220-300 B/clk per SM when measured alone, plus two more barrier
+// hops per unit). A register-operand mma.sync takes the dequantised pairs where
+// they are made.
 //
 // Two CTAs per SM of 8 warps each, no producer warp and no spin-wait anywhere:
 //   * all threads copy unit u+S-1 with cp.async (16 B each, rows of 256 contiguous
